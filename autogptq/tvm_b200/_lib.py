@@ -1,0 +1,74 @@
+"""ctypes binding of ``libb200gptq.so`` (the C ABI declared in ``include/b200gptq.h``).
+
+There is no fallback: if the shared library is absent and cannot be built, importing
+this module raises, and every operator of the package fails with it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+OP_GEMV = 1
+OP_GEMM = 2
+
+_c_int = ctypes.c_int
+_c_void_p = ctypes.c_void_p
+_c_size_t = ctypes.c_size_t
+
+_SIGNATURES = {
+    "b200gptq_strerror": (ctypes.c_char_p, [_c_int]),
+    "b200gptq_last_cuda_error": (_c_int, []),
+    "b200gptq_abi_version": (_c_int, []),
+    "b200gptq_dequant": (_c_int, [_c_void_p] * 4 + [_c_int] * 4 + [_c_void_p] * 3),
+    "b200gptq_workspace_bytes": (_c_size_t, [_c_int] * 5),
+    "b200gptq_gemv": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
+    "b200gptq_gemm": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
+    "b200gptq_sort_rows": (_c_int, [_c_void_p] * 3 + [_c_int] * 3 + [_c_void_p] * 3),
+}
+
+
+def _load() -> ctypes.CDLL:
+    path = _build.LIB_PATH
+    if not os.path.isfile(path) or (_build.is_stale() and _build_possible()):
+        if not _build_possible():
+            raise ImportError(
+                f"{path} is missing and nvcc is not available to build it; "
+                "the B200 GPTQ kernels have no fallback implementation")
+        _build.build()
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means the library does not match the header
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+def _build_possible() -> bool:
+    import shutil
+    return bool(shutil.which("nvcc")) or os.path.exists("/usr/local/cuda/bin/nvcc")
+
+
+lib = _load()
+LIB_PATH = _build.LIB_PATH
+
+
+class B200GPTQError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib.b200gptq_strerror(status).decode()
+        if status == -6:
+            msg += f" (cudaError {lib.b200gptq_last_cuda_error()})"
+        super().__init__(f"{where}: {msg} [status {status}]")
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        if status in (-2, -3, -4):
+            raise ValueError(str(B200GPTQError(status, where)))
+        raise B200GPTQError(status, where)
+
+
+def workspace_bytes(op: int, M: int, K: int, N: int, bits: int) -> int:
+    return int(lib.b200gptq_workspace_bytes(op, M, K, N, bits))

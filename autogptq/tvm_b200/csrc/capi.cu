@@ -1,0 +1,150 @@
+// extern "C" boundary: argument validation and dispatch.  See include/b200gptq.h.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace b200gptq {
+
+static thread_local int tls_last_cuda_error = 0;
+void set_last_cuda_error(int err) { tls_last_cuda_error = err; }
+
+int sm_count() {
+    static std::mutex mu;
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// implemented in the kernel translation units
+int dequant_dispatch(const int32_t*, const int32_t*, const __half*, const int32_t*, int, int, int, int, int8_t*,
+                     __half*, cudaStream_t);
+int sort_rows_dispatch(const int32_t*, const int32_t*, const int32_t*, int, int, int, int32_t*, int32_t*,
+                       cudaStream_t);
+int gemv_generic_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*,
+                          const int32_t*, const __half*, __half*, int, int, int, int, int, void*, cudaStream_t);
+size_t gemv_generic_workspace_bytes(int M, int K, int N);
+bool gemv_stream_supported(int M, int K, int N, int bits, int group_size);
+size_t gemv_stream_workspace_bytes(int M, int K, int N, int bits);
+int gemv_stream_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*,
+                         const int32_t*, const __half*, __half*, int, int, int, int, int, void*, cudaStream_t);
+size_t gemm_workspace_bytes(int M, int K, int N, int bits);
+int gemm_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*, const int32_t*,
+                  const __half*, __half*, int, int, int, int, int, void*, size_t, cudaStream_t);
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Packing rules shared by every entry point.
+static int check_layer(int K, int N, int bits, int* group_size) {
+    if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return B200GPTQ_ERR_BITS;
+    if (K <= 0 || N <= 0 || K % 32 != 0) return B200GPTQ_ERR_SHAPE;
+    if (N % 8 != 0 || (bits == 3 && N % 32 != 0)) return B200GPTQ_ERR_SHAPE;
+    if (*group_size == -1) *group_size = K;
+    if (*group_size <= 0) return B200GPTQ_ERR_SHAPE;
+    return B200GPTQ_OK;
+}
+
+}  // namespace b200gptq
+
+using namespace b200gptq;
+
+extern "C" {
+
+const char* b200gptq_strerror(int status) {
+    switch (status) {
+        case B200GPTQ_OK: return "ok";
+        case B200GPTQ_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case B200GPTQ_ERR_BITS: return "unsupported bit width for this entry point";
+        case B200GPTQ_ERR_SHAPE: return "K, N, M or group_size violate the packing rules (K % 32, N % 8, N % 32 for 3-bit)";
+        case B200GPTQ_ERR_ALIGNMENT: return "a device pointer is not 16-byte aligned";
+        case B200GPTQ_ERR_WORKSPACE: return "workspace missing or smaller than b200gptq_workspace_bytes()";
+        case B200GPTQ_ERR_CUDA: return "CUDA runtime error; see b200gptq_last_cuda_error()";
+        case B200GPTQ_ERR_GROUPS: return "g_idx must be constant over aligned 32-row blocks for this entry point";
+        case B200GPTQ_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point";
+    }
+    return "unknown status";
+}
+
+int b200gptq_last_cuda_error(void) { return tls_last_cuda_error; }
+
+int b200gptq_abi_version(void) { return 1; }
+
+int b200gptq_dequant(const int32_t* qweight, const int32_t* qzeros, const void* scales, const int32_t* g_idx,
+                     int K, int N, int bits, int group_size, int8_t* q_out, void* w_out, void* stream) {
+    if (!qweight || !qzeros || !scales) return B200GPTQ_ERR_NULL_POINTER;
+    if (int st = check_layer(K, N, bits, &group_size)) return st;
+    if (bits == 8 && q_out) return B200GPTQ_ERR_BITS;
+    if (!aligned16(qweight) || (w_out && !aligned16(w_out)) || (q_out && !aligned16(q_out)) ||
+        (reinterpret_cast<uintptr_t>(scales) & 7u))
+        return B200GPTQ_ERR_ALIGNMENT;
+    if (!q_out && !w_out) return B200GPTQ_OK;
+    return dequant_dispatch(qweight, qzeros, static_cast<const __half*>(scales), g_idx, K, N, bits, group_size,
+                            q_out, static_cast<__half*>(w_out), static_cast<cudaStream_t>(stream));
+}
+
+int b200gptq_sort_rows(const int32_t* qweight, const int32_t* g_idx, const int32_t* perm, int K, int N, int bits,
+                       int32_t* qweight_sorted, int32_t* g_idx_sorted, void* stream) {
+    if (!qweight || !perm || !qweight_sorted || !g_idx) return B200GPTQ_ERR_NULL_POINTER;
+    int gs = K;
+    if (int st = check_layer(K, N, bits, &gs)) return st;
+    if (!aligned16(qweight) || !aligned16(qweight_sorted)) return B200GPTQ_ERR_ALIGNMENT;
+    return sort_rows_dispatch(qweight, g_idx, perm, K, N, bits, qweight_sorted, g_idx_sorted,
+                              static_cast<cudaStream_t>(stream));
+}
+
+size_t b200gptq_workspace_bytes(int op, int M, int K, int N, int bits) {
+    if (M <= 0 || K <= 0 || N <= 0) return 0;
+    if (op == B200GPTQ_OP_GEMV) {
+        size_t a = gemv_generic_workspace_bytes(M, K, N);
+        size_t b = gemv_stream_workspace_bytes(M, K, N, bits);
+        return a > b ? a : b;
+    }
+    if (op == B200GPTQ_OP_GEMM) return gemm_workspace_bytes(M, K, N, bits);
+    return 0;
+}
+
+int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                  const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
+                  int bits, int group_size, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !qweight || !qzeros || !scales || !y) return B200GPTQ_ERR_NULL_POINTER;
+    if (int st = check_layer(K, N, bits, &group_size)) return st;
+    if (M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
+    if (!aligned16(qweight) || !aligned16(x) || !aligned16(y) || !aligned16(scales) || !aligned16(qzeros))
+        return B200GPTQ_ERR_ALIGNMENT;
+    if (!workspace || workspace_bytes < b200gptq_workspace_bytes(B200GPTQ_OP_GEMV, M, K, N, bits))
+        return B200GPTQ_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return B200GPTQ_ERR_ALIGNMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (gemv_stream_supported(M, K, N, bits, group_size))
+        return gemv_stream_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
+                                    g_idx, x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K,
+                                    N, bits, group_size, workspace, st);
+    return gemv_generic_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
+                                 g_idx, x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K, N,
+                                 bits, group_size, workspace, st);
+}
+
+int b200gptq_gemm(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                  const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
+                  int bits, int group_size, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !qweight || !qzeros || !scales || !y) return B200GPTQ_ERR_NULL_POINTER;
+    if (int st = check_layer(K, N, bits, &group_size)) return st;
+    if (bits != 3 && bits != 4) return B200GPTQ_ERR_BITS;
+    if (M < 1) return B200GPTQ_ERR_SHAPE;
+    if (!aligned16(qweight) || !aligned16(x) || !aligned16(y) || !aligned16(scales) || !aligned16(qzeros))
+        return B200GPTQ_ERR_ALIGNMENT;
+    const size_t need = b200gptq_workspace_bytes(B200GPTQ_OP_GEMM, M, K, N, bits);
+    if (need && (!workspace || workspace_bytes < need)) return B200GPTQ_ERR_WORKSPACE;
+    if (workspace && !aligned16(workspace)) return B200GPTQ_ERR_ALIGNMENT;
+    return gemm_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales), g_idx,
+                         x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K, N, bits,
+                         group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

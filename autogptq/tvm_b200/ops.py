@@ -1,0 +1,137 @@
+"""Functional wrappers: torch CUDA tensors in, C-ABI calls out.
+
+Each function validates what the C side cannot see (device, dtype, contiguity),
+passes raw device pointers plus the current CUDA stream, and raises on a non-zero
+status.  Nothing here computes on the host.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_workspaces = {}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: the B200 GPTQ kernels have no CPU path")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch shared by the calls issued on one device.
+
+    The kernels restore the scratch to its zero state, so one buffer serves every
+    layer as long as calls are ordered on a stream.  Callers that run layers
+    concurrently on several streams must pass their own workspace instead.
+    """
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(nbytes, 1 << 20)
+        ws = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def layer_dims(qweight: torch.Tensor, bits: int) -> Tuple[int, int]:
+    return qweight.shape[0] * 32 // bits, qweight.shape[1]
+
+
+def dequantize(qweight, qzeros, scales, g_idx, bits: int, group_size: int,
+               want_q: bool = True, want_w: bool = True):
+    """Return ``(q int8 [K,N] | None, W fp16 [K,N] | None)`` computed on the GPU."""
+    _need_cuda("qweight", qweight, torch.int32)
+    _need_cuda("qzeros", qzeros, torch.int32)
+    _need_cuda("scales", scales, torch.float16)
+    if g_idx is not None:
+        _need_cuda("g_idx", g_idx, torch.int32)
+    K, N = layer_dims(qweight, bits)
+    dev = qweight.device
+    q = torch.empty((K, N), dtype=torch.int8, device=dev) if want_q else None
+    w = torch.empty((K, N), dtype=torch.float16, device=dev) if want_w else None
+    with torch.cuda.device(dev):
+        st = _lib.lib.b200gptq_dequant(_ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), K, N, bits,
+                                       group_size, _ptr(q), _ptr(w), _stream(dev))
+    _lib.check(st, "b200gptq_dequant")
+    return q, w
+
+
+def sort_rows(qweight, g_idx, bits: int):
+    """Re-order the rows of an act-order layer by group.  Returns
+    ``(qweight_sorted, perm, g_idx_sorted)``; ``perm`` is the stable argsort of ``g_idx``."""
+    _need_cuda("qweight", qweight, torch.int32)
+    _need_cuda("g_idx", g_idx, torch.int32)
+    K, N = layer_dims(qweight, bits)
+    perm = torch.sort(g_idx.to(torch.int64), stable=True).indices.to(torch.int32).contiguous()
+    out = torch.empty_like(qweight)
+    g_sorted = torch.empty_like(g_idx)
+    dev = qweight.device
+    with torch.cuda.device(dev):
+        st = _lib.lib.b200gptq_sort_rows(_ptr(qweight), _ptr(g_idx), _ptr(perm), K, N, bits, _ptr(out),
+                                         _ptr(g_sorted), _stream(dev))
+    _lib.check(st, "b200gptq_sort_rows")
+    return out, perm, g_sorted
+
+
+def _matmul(fn_name: str, op: int, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits, group_size,
+            out, workspace):
+    _need_cuda("x", x, torch.float16)
+    _need_cuda("qweight", qweight, torch.int32)
+    _need_cuda("qzeros", qzeros, torch.int32)
+    _need_cuda("scales", scales, torch.float16)
+    if g_idx is not None:
+        _need_cuda("g_idx", g_idx, torch.int32)
+    if x_perm is not None:
+        _need_cuda("x_perm", x_perm, torch.int32)
+    if bias is not None:
+        _need_cuda("bias", bias, torch.float16)
+    K, N = layer_dims(qweight, bits)
+    if x.dim() != 2 or x.shape[1] != K:
+        raise ValueError(f"x must be [M, {K}], got {tuple(x.shape)}")
+    M = x.shape[0]
+    dev = x.device
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    else:
+        _need_cuda("out", out, torch.float16)
+        if tuple(out.shape) != (M, N):
+            raise ValueError(f"out must be [{M}, {N}]")
+    need = _lib.workspace_bytes(op, M, K, N, bits)
+    if workspace is None:
+        workspace = get_workspace(dev, need)
+    with torch.cuda.device(dev):
+        st = getattr(_lib.lib, fn_name)(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
+                                        _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
+                                        _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                        _stream(dev))
+    _lib.check(st, fn_name)
+    return out
+
+
+def gemv(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None,
+         out=None, workspace=None):
+    """Decode GEMV, ``x`` fp16 ``[M<=8, K]`` -> fp16 ``[M, N]``."""
+    return _matmul("b200gptq_gemv", _lib.OP_GEMV, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits,
+                   group_size, out, workspace)
+
+
+def gemm(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None,
+         out=None, workspace=None):
+    """Prefill dequant-GEMM on tcgen05, ``x`` fp16 ``[M, K]`` -> fp16 ``[M, N]``."""
+    return _matmul("b200gptq_gemm", _lib.OP_GEMM, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits,
+                   group_size, out, workspace)

@@ -1,0 +1,161 @@
+"""``QuantLinear`` -- the module that ``make_quant(..., use_tvm=True)`` installs.
+
+Mirrors the constructor / ``pack`` / ``forward`` surface of the reference's TVM
+module (``auto_gptq/nn_modules/qlinear_tvm.py:10-158``) but keeps the standard
+AutoGPTQ buffers of ``auto_gptq/nn_modules/qlinear.py:40-59`` (``qweight``,
+``qzeros``, ``scales``, ``g_idx``, ``bias``), so ordinary GPTQ checkpoints load
+unchanged.  ``forward`` runs on the GPU only: M <= 8 rows go to the decode GEMV,
+more rows to the tcgen05 dequant-GEMM.  There is no M padding, no per-shape
+kernel cache and no tuner (the reference's ``tvm_untils/cache.py`` and
+``pycuda_warpper.py`` have no counterpart here).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import ops
+
+GEMV_MAX_M = 8
+
+
+def _pack_fields(vals: torch.Tensor, bits: int) -> torch.Tensor:
+    """Pack ``vals`` (int64 ``[R, C]``, R % 32 == 0) along dim 0 into int32 words.
+
+    2/4/8 bits: field j of a word at bit ``bits*j``.  3 bits: 32 fields form a
+    96-bit little-endian stream over three words.  Over-wide values spill into
+    the neighbouring fields exactly like the reference's un-masked ``|=``
+    (qlinear.py:111-134).
+    """
+    R, C = vals.shape
+    if bits in (2, 4, 8):
+        pf = 32 // bits
+        v = vals.reshape(R // pf, pf, C)
+        shifts = (torch.arange(pf, dtype=torch.int64) * bits).reshape(1, pf, 1)
+        words = torch.zeros((R // pf, C), dtype=torch.int64)
+        for j in range(pf):
+            words |= (v[:, j] << (bits * j)) & 0xFFFFFFFF
+        del shifts
+    else:
+        v = vals.reshape(R // 32, 32, C)
+        words = torch.zeros((R // 32, 3, C), dtype=torch.int64)
+        for j in range(32):
+            bit = 3 * j
+            wi, sh = bit // 32, bit % 32
+            words[:, wi] |= (v[:, j] << sh) & 0xFFFFFFFF
+            if sh > 29:  # the field straddles into the next word
+                mask = (1 << (sh + 3 - 32)) - 1
+                words[:, wi + 1] |= (v[:, j] >> (32 - sh)) & mask
+        words = words.reshape(R // 32 * 3, C)
+    words = torch.where(words >= 2**31, words - 2**32, words)
+    return words.to(torch.int32)
+
+
+class QuantLinear(nn.Module):
+    def __init__(self, bits, groupsize, infeatures, outfeatures, bias):
+        super().__init__()
+        if bits not in [2, 3, 4, 8]:
+            raise NotImplementedError("Only 2,3,4,8 bits are supported.")
+        if infeatures % 32 != 0 or outfeatures % 8 != 0 or (bits == 3 and outfeatures % 32 != 0):
+            raise ValueError("infeatures must be a multiple of 32 and outfeatures of 8 (32 for 3-bit)")
+        self.infeatures = infeatures
+        self.outfeatures = outfeatures
+        self.bits = bits
+        self.groupsize = groupsize if groupsize != -1 else infeatures
+        self.maxq = 2 ** self.bits - 1
+        G = math.ceil(infeatures / self.groupsize)
+        self.register_buffer("qweight", torch.zeros((infeatures // 32 * bits, outfeatures), dtype=torch.int32))
+        self.register_buffer("qzeros", torch.zeros((G, outfeatures // 32 * bits), dtype=torch.int32))
+        self.register_buffer("scales", torch.zeros((G, outfeatures), dtype=torch.float16))
+        self.register_buffer("g_idx", (torch.arange(infeatures, dtype=torch.int64) // self.groupsize).to(torch.int32))
+        if bias:
+            self.register_buffer("bias", torch.zeros((outfeatures,), dtype=torch.float16))
+        else:
+            self.bias = None
+        # derived, non-persistent state built by post_init() on the device
+        self._ready_for = None
+        self._qweight_run = None   # the weights the kernels read: qweight itself or its row-sorted copy
+        self._g_idx_run = None     # None => rows use group k // groupsize
+        self._x_perm = None        # None => no gather of x
+
+    # ---- offline packing (CPU) ----------------------------------------------------------
+    def pack(self, linear, scales, zeros, g_idx=None):
+        """Same contract as ``QuantLinear.pack`` of the reference (qlinear.py:77-175):
+        ``scales`` / ``zeros`` are ``[outfeatures, G]``; the integer weight is
+        ``round((W + zero*scale) / fp16(scale))`` per row group and ``zeros - 1`` is stored."""
+        W = linear.weight.data.clone()
+        if isinstance(linear, nn.Conv2d):
+            W = W.flatten(1)
+        elif type(linear).__name__ == "Conv1D":  # transformers.pytorch_utils.Conv1D keeps [in, out]
+            W = W.t()
+        self.g_idx = g_idx.clone() if g_idx is not None else self.g_idx
+        g = self.g_idx.long()
+        scales = scales.t().contiguous()
+        zeros = zeros.t().contiguous()
+        scale_zeros = zeros * scales
+        self.scales = scales.clone().half()
+        if linear.bias is not None:
+            self.bias = linear.bias.detach().clone().half()
+        intweight = torch.round((W.t() + scale_zeros[g]) / self.scales[g]).to(torch.int)
+        intweight = torch.from_numpy(intweight.numpy().astype(np.uint32).astype(np.int64))
+        self.qweight = _pack_fields(intweight, self.bits)
+        zq = torch.from_numpy((zeros - 1).numpy().astype(np.uint32).astype(np.int64))
+        self.qzeros = _pack_fields(zq.t().contiguous(), self.bits).t().contiguous()
+        self._ready_for = None
+
+    # ---- device-side preparation ----------------------------------------------------------
+    def post_init(self):
+        """Build the run-time view of the layer on its current device.
+
+        A layer whose ``g_idx`` is constant over every aligned block of 32 rows is
+        used as stored.  Any other ``g_idx`` (act-order checkpoints) is re-ordered
+        once so that rows of a group are adjacent; ``forward`` then gathers ``x``
+        through the permutation inside the kernels.
+        """
+        dev = self.qweight.device
+        if dev.type != "cuda":
+            raise RuntimeError("QuantLinear.post_init needs the module on a CUDA device")
+        K = self.infeatures
+        g = self.g_idx
+        trivial = torch.equal(g, (torch.arange(K, device=dev, dtype=torch.int64) // self.groupsize).to(torch.int32))
+        blocks = g.view(K // 32, 32)
+        block_uniform = bool((blocks == blocks[:, :1]).all().item())
+        if trivial:
+            self._qweight_run, self._g_idx_run, self._x_perm = self.qweight, None, None
+        elif block_uniform:
+            self._qweight_run, self._g_idx_run, self._x_perm = self.qweight, g.contiguous(), None
+        else:
+            qs, perm, gs = ops.sort_rows(self.qweight.contiguous(), g.contiguous(), self.bits)
+            sorted_trivial = torch.equal(
+                gs, (torch.arange(K, device=dev, dtype=torch.int64) // self.groupsize).to(torch.int32))
+            self._qweight_run, self._x_perm = qs, perm
+            self._g_idx_run = None if sorted_trivial else gs
+        self._ready_for = (dev, self.qweight.data_ptr(), self.g_idx.data_ptr())
+
+    def _ready(self) -> bool:
+        return self._ready_for == (self.qweight.device, self.qweight.data_ptr(), self.g_idx.data_ptr())
+
+    # ---- forward --------------------------------------------------------------------------
+    def forward(self, x):
+        if not x.is_cuda:
+            raise RuntimeError("QuantLinear.forward needs CUDA tensors: this backend has no CPU path")
+        if not self._ready():
+            self.post_init()
+        out_shape = x.shape[:-1] + (self.outfeatures,)
+        x2 = x.half().reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        fn = ops.gemv if x2.shape[0] <= GEMV_MAX_M else ops.gemm
+        y = fn(x2, self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize,
+               bias=self.bias, x_perm=self._x_perm)
+        return y.reshape(out_shape)
+
+    def extra_repr(self):
+        return (f"in={self.infeatures}, out={self.outfeatures}, bits={self.bits}, "
+                f"groupsize={self.groupsize}, bias={self.bias is not None}")
+
+
+__all__ = ["QuantLinear"]

@@ -1,0 +1,135 @@
+/*
+ * b200gptq -- C ABI of the B200 (sm_100a) GPTQ QuantLinear forward kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * caller's stream, never synchronises, never allocates device memory, and
+ * returns 0 on success or a negative B200GPTQ_ERR_* code.  Nothing throws,
+ * aborts or prints.  All buffers are owned by the caller.
+ *
+ * Buffer formats are the standard AutoGPTQ ones
+ * (auto_gptq/nn_modules/qlinear.py:40-59 of the reference):
+ *   qweight int32 [K/32*bits, N]   row-major, fields packed along K
+ *   qzeros  int32 [G, N/32*bits]   fields packed along N, stored value = zero - 1
+ *   scales  fp16  [G, N]
+ *   g_idx   int32 [K]              group of row k; NULL means k / group_size
+ *   bias    fp16  [N] or NULL
+ *   x       fp16  [M, K], y fp16 [M, N], both row-major and dense
+ * with G = ceil(K / group_size) (group_size == -1 means one group, G = 1).
+ *
+ * These functions replace, for the reference, the per-shape kernel handler
+ * `handler(x, qweight, y, scales, zeros)` that
+ * auto_gptq/nn_modules/tvm_untils/pycuda_warpper.py:138-189 builds with TVM and
+ * launches through pycuda, and the dequantise-then-matmul arithmetic of
+ * auto_gptq/nn_modules/qlinear.py:197-243 that defines its results.
+ */
+#ifndef B200GPTQ_H_
+#define B200GPTQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define B200GPTQ_API __attribute__((visibility("default")))
+#else
+#define B200GPTQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200GPTQ_OK 0
+#define B200GPTQ_ERR_NULL_POINTER (-1)   /* a required pointer is NULL */
+#define B200GPTQ_ERR_BITS (-2)           /* bits not supported by this entry point */
+#define B200GPTQ_ERR_SHAPE (-3)          /* K, N, M or group_size violate the packing rules */
+#define B200GPTQ_ERR_ALIGNMENT (-4)      /* a pointer is not 16-byte aligned */
+#define B200GPTQ_ERR_WORKSPACE (-5)      /* workspace missing or smaller than b200gptq_workspace_bytes() */
+#define B200GPTQ_ERR_CUDA (-6)           /* the CUDA runtime refused the launch; see b200gptq_last_cuda_error() */
+#define B200GPTQ_ERR_GROUPS (-7)         /* this entry point needs g_idx constant over aligned 32-row blocks */
+#define B200GPTQ_ERR_TOO_LARGE (-8)      /* the problem exceeds a fixed capacity of this entry point */
+
+/* op selectors of b200gptq_workspace_bytes() */
+#define B200GPTQ_OP_GEMV 1
+#define B200GPTQ_OP_GEMM 2
+
+/* Text for a status code.  Never NULL. */
+B200GPTQ_API const char* b200gptq_strerror(int status);
+
+/* cudaError_t of the most recent B200GPTQ_ERR_CUDA on the calling thread (0 if none). */
+B200GPTQ_API int b200gptq_last_cuda_error(void);
+
+/* ABI version; bumped when a signature changes. */
+B200GPTQ_API int b200gptq_abi_version(void);
+
+/*
+ * Unpack and dequantise a whole layer.
+ *   q_out  int8 [K, N]  (nullable)  q[k,n], the integer field
+ *   w_out  fp16 [K, N]  (nullable)  W[k,n] = scales[g,n] * fp16(q[k,n] - (qzeros_field[g,n] + 1)),
+ *                                   g = g_idx[k]; one fp16 rounding, no flush-to-zero
+ * bits in {2,3,4,8} (q_out must be NULL for 8 bits).  Bit-exact restatement of the
+ * unpack / dequantise half of qlinear.py:201-242.
+ */
+B200GPTQ_API int b200gptq_dequant(const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                     const int32_t* g_idx, int K, int N, int bits, int group_size,
+                     int8_t* q_out, void* w_out, void* stream);
+
+/*
+ * Bytes of scratch that b200gptq_gemv / b200gptq_gemm may use for this problem.
+ * The scratch must be zero-filled once before its first use; the kernels leave
+ * it zero-filled where that matters, so one buffer can serve every later call
+ * on the same stream.  Calls that may overlap on the GPU need separate buffers.
+ */
+B200GPTQ_API size_t b200gptq_workspace_bytes(int op, int M, int K, int N, int bits);
+
+/*
+ * Decode GEMV, 1 <= M <= 8:  y[m,:] = x[m,:] @ W (+ bias), fp32 accumulation,
+ * fp16 result.  bits in {2,3,4,8}.  Replaces the TVM `m1` kernel launch of
+ * pycuda_warpper.py:144-149 (kernel: src/kernels/gemv_kernel.cu:25-55).
+ *
+ *   x_perm  int32 [K] or NULL.  When given, row r of qweight multiplies
+ *           x[m, x_perm[r]] instead of x[m, r]: this is how a layer whose rows
+ *           were re-ordered by b200gptq_sort_rows() is evaluated.
+ *
+ * Any g_idx is accepted.  Rows whose aligned 32-row block shares one group take
+ * the streaming path; other blocks take a slower per-row path.
+ */
+B200GPTQ_API int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                  const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
+                  int M, int K, int N, int bits, int group_size,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Prefill GEMM, any M >= 1 (meant for M >= 16):  y = x @ W (+ bias) on the
+ * tcgen05 tensor cores with fp32 accumulators in tensor memory.  bits in {3,4}.
+ * Replaces the TVM `m16 .. m256` kernel launches of pycuda_warpper.py:150-189
+ * (kernels: src/kernels/gemm_kernel.cu:25-142); no M padding is needed.
+ *
+ * x_perm as for b200gptq_gemv, except that a non-NULL x_perm needs
+ * workspace room for the gathered copy of x (counted by b200gptq_workspace_bytes).
+ * g_idx must be constant over aligned 32-row blocks (B200GPTQ_ERR_GROUPS
+ * otherwise is reported through *status_word, see below); layers with an
+ * arbitrary act-order g_idx are first re-ordered with b200gptq_sort_rows().
+ */
+B200GPTQ_API int b200gptq_gemm(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                  const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
+                  int M, int K, int N, int bits, int group_size,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Re-order the rows of a packed layer so that rows of one group are adjacent
+ * (stable sort of k by g_idx[k]).  Outputs:
+ *   qweight_sorted int32 [K/32*bits, N]   row r holds original row perm[r]
+ *   perm           int32 [K]              the x_perm to pass to gemv / gemm
+ *   g_idx_sorted   int32 [K]              g_idx[perm[r]], non-decreasing
+ * `perm` is computed by the caller (it is a host-side argsort of g_idx) and
+ * read here from device memory; this entry point does the unpack / gather /
+ * repack of the weight fields, bits in {2,3,4,8}.
+ */
+B200GPTQ_API int b200gptq_sort_rows(const int32_t* qweight, const int32_t* g_idx, const int32_t* perm,
+                       int K, int N, int bits,
+                       int32_t* qweight_sorted, int32_t* g_idx_sorted, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GPTQ_H_ */

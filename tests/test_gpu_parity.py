@@ -1,0 +1,200 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle.
+
+Integer fields and dequantised fp16 weights must match bit for bit; outputs must
+lie within ``1e-2 * ||x||_2 * max|w|`` of an fp64 product of the same dequantised
+weights (the contract), and additionally within a much tighter band that an
+fp32-accumulating kernel with an fp16 result is expected to meet.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_DIR, golden_files
+from oracle import gptq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from autogptq.tvm_b200 import QuantLinear, ops, synth, _lib
+    DEV = torch.device("cuda:0")
+
+
+def _bits16(a):
+    return (np.asarray(a, np.float16) + np.float16(0)).view(np.uint16)
+
+
+def _check_output(y, x, W, bias=None, tight=True):
+    ref = O.forward_fp64(x, W, bias)
+    got = y.detach().cpu().numpy().astype(np.float64).reshape(ref.shape)
+    err = np.abs(got - ref)
+    tol = O.output_tolerance(x, W)  # contract: 1e-2 * ||x||_2 * max|w| per output
+    assert np.all(err <= tol), f"contract tolerance exceeded: max err {err.max()} tol {tol.min()}"
+    if tight:
+        # fp32 accumulation + one fp16 rounding of the result
+        band = 2.0 ** -10 * np.abs(ref) + 0.05 * tol
+        assert np.all(err <= band), f"max err {err.max()} exceeds the fp32-accumulate band"
+
+
+def _layer_np(layer):
+    return (layer.qweight.cpu().numpy(), layer.qzeros.cpu().numpy(), layer.scales.cpu().numpy(),
+            layer.g_idx.cpu().numpy())
+
+
+def test_library_is_loaded_from_the_tree():
+    assert os.path.isfile(_lib.LIB_PATH)
+    assert _lib.lib.b200gptq_abi_version() >= 1
+
+
+@pytest.mark.parametrize("fname", golden_files("forward_"))
+def test_dequant_bit_exact_on_reference_vectors(fname):
+    g = dict(np.load(os.path.join(GOLDEN_DIR, fname)))
+    bits, gs = int(g["bits"]), int(g["group_size"])
+    t = lambda a: torch.from_numpy(a).to(DEV)
+    q, W = ops.dequantize(t(g["qweight"]), t(g["qzeros"]), t(g["scales"]), t(g["g_idx"]), bits, gs,
+                          want_q=(bits != 8))
+    assert np.array_equal(_bits16(W.cpu().numpy()), _bits16(g["W"]))
+    if bits != 8:
+        assert np.array_equal(q.cpu().numpy(), O.unpack_qweight(g["qweight"], bits))
+
+
+@pytest.mark.parametrize("bits,K,N,gs,act", [
+    (4, 1024, 512, 128, False), (3, 1024, 512, 128, True), (4, 2048, 1056, 64, True),
+    (3, 512, 96, -1, False), (2, 256, 64, 32, True), (8, 256, 72, 128, False), (4, 32, 8, 32, False),
+])
+def test_dequant_bit_exact_seeded(bits, K, N, gs, act):
+    layer = synth.make_layer(bits, K, N, gs, act, seed=bits * 100 + N)
+    q_ref, z_ref, W_ref = O.dequantize(*_layer_np(layer), bits)
+    d = layer.to(DEV)
+    q, W = ops.dequantize(d.qweight, d.qzeros, d.scales, d.g_idx, bits, gs, want_q=(bits != 8))
+    assert np.array_equal(_bits16(W.cpu().numpy()), _bits16(W_ref))
+    if bits != 8:
+        assert np.array_equal(q.cpu().numpy(), q_ref)
+    # g_idx = NULL means k // group_size
+    if not act:
+        _, W2 = ops.dequantize(d.qweight, d.qzeros, d.scales, None, bits, gs, want_q=False)
+        assert torch.equal(W2, W)
+
+
+@pytest.mark.parametrize("fname", golden_files("forward_"))
+def test_quantlinear_forward_on_reference_vectors(fname):
+    g = dict(np.load(os.path.join(GOLDEN_DIR, fname)))
+    bits, gs = int(g["bits"]), int(g["group_size"])
+    K, N = g["W"].shape
+    has_bias = g["bias"].size > 0
+    layer = QuantLinear(bits, gs, K, N, has_bias)
+    layer.qweight = torch.from_numpy(g["qweight"])
+    layer.qzeros = torch.from_numpy(g["qzeros"])
+    layer.scales = torch.from_numpy(g["scales"])
+    layer.g_idx = torch.from_numpy(g["g_idx"])
+    if has_bias:
+        layer.bias = torch.from_numpy(g["bias"])
+    layer = layer.to(DEV)
+    y = layer(torch.from_numpy(g["x"]).to(DEV))
+    assert y.dtype == torch.float16 and tuple(y.shape) == g["out"].shape
+    _check_output(y, g["x"], g["W"], g["bias"] if has_bias else None)
+    # and close to what the reference itself returned (its fp16 matmul rounds differently)
+    assert np.max(np.abs(y.cpu().numpy().astype(np.float32) - g["out"].astype(np.float32))) <= 3e-2
+
+
+GEMV_CASES = [
+    # bits, K, N, gs, act, bias
+    (4, 1024, 512, 128, False, False),
+    (4, 4096, 4096, 128, False, False),       # config 0
+    (3, 4096, 11008, 128, True, False),       # config 1
+    (3, 1024, 512, 128, False, True),
+    (4, 2048, 1056, 64, True, True),          # N not a multiple of the strip width
+    (4, 11008, 4096, 128, False, False),      # Llama down_proj
+    (3, 512, 96, -1, False, False),
+    (2, 256, 64, 32, True, False),
+    (8, 256, 72, 128, False, True),
+    (4, 32, 8, 32, False, False),             # smallest legal layer
+]
+
+
+@pytest.mark.parametrize("bits,K,N,gs,act,bias", GEMV_CASES)
+@pytest.mark.parametrize("M", [1, 2, 5, 8])
+def test_gemv_vs_oracle(bits, K, N, gs, act, bias, M):
+    if M not in (1, 8) and K * N > 4096 * 4096:
+        pytest.skip("large shapes are covered at M = 1 and 8")
+    layer = synth.make_layer(bits, K, N, gs, act, bias=bias, seed=K + N + bits)
+    x = synth.make_x(M, K, seed=M)
+    _, _, W = O.dequantize(*_layer_np(layer), bits)
+    d = layer.to(DEV)
+    y = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, d.g_idx, bits, gs, bias=d.bias)
+    _check_output(y, x.numpy(), W, None if layer.bias is None else layer.bias.numpy())
+    y2 = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, d.g_idx, bits, gs, bias=d.bias)
+    assert torch.equal(y, y2), "two runs on the same inputs must agree bit for bit"
+
+
+@pytest.mark.parametrize("bits,K,N,gs", [(4, 4096, 4096, 128), (3, 4096, 11008, 128), (4, 1024, 520, 64)])
+@pytest.mark.parametrize("M", [1, 4])
+def test_sorted_rows_path_matches_oracle(bits, K, N, gs, M):
+    """Act-order layer evaluated through QuantLinear: rows re-ordered by group, x gathered."""
+    layer = synth.make_layer(bits, K, N, gs, act_order=True, seed=11 + bits)
+    _, _, W = O.dequantize(*_layer_np(layer), bits)
+    d = layer.to(DEV)
+    qs, perm, g_sorted = ops.sort_rows(d.qweight, d.g_idx, bits)
+    assert torch.equal(g_sorted, d.g_idx[perm.long()])
+    assert bool((g_sorted[1:] >= g_sorted[:-1]).all())
+    _, Ws = ops.dequantize(qs, d.qzeros, d.scales, g_sorted, bits, gs, want_q=False)
+    assert np.array_equal(_bits16(Ws.cpu().numpy()), _bits16(W[perm.cpu().numpy()]))
+    x = synth.make_x(M, K, seed=3)
+    y = ops.gemv(x.to(DEV), qs, d.qzeros, d.scales, g_sorted, bits, gs, x_perm=perm)
+    _check_output(y, x.numpy(), W)
+    mod = QuantLinear(bits, gs, K, N, False)
+    mod.qweight, mod.qzeros, mod.scales, mod.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
+    mod = mod.to(DEV)
+    _check_output(mod(x.to(DEV)), x.numpy(), W)
+    assert mod._x_perm is not None
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+def test_known_answer_integer_sums(bits):
+    """w = arange % 4, x = ones, scale = 1, zero-point 1 (the reference's hand-run pattern,
+    pycuda_warpper.py:330-343): every output is an exactly representable integer sum."""
+    K, N = 1024, 256
+    w = (np.arange(N * K, dtype=np.int64) % 4).reshape(N, K).astype(np.float32)
+    qweight, qzeros, s16 = O.pack(w, np.ones((N, 1), np.float32), np.ones((N, 1), np.float32),
+                                  np.zeros(K, np.int32), bits)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    x = torch.ones((1, K), dtype=torch.float16, device=DEV)
+    y = ops.gemv(x, t(qweight), t(qzeros), t(s16), None, bits, -1)
+    assert np.array_equal(y.cpu().numpy().astype(np.float64)[0], w.sum(axis=1))
+
+
+def test_linearity_at_full_size():
+    """Size-independent property on config 1: y(a + b) = y(a) + y(b) up to fp16 rounding of the outputs."""
+    layer = synth.make_layer(3, 4096, 11008, 128, True, seed=5).to(DEV)
+    mod = QuantLinear(3, 128, 4096, 11008, False)
+    mod.qweight, mod.qzeros, mod.scales, mod.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
+    mod = mod.to(DEV)
+    a = (synth.make_x(1, 4096, seed=1) * 0.5).to(DEV)
+    b = (synth.make_x(1, 4096, seed=2) * 0.5).to(DEV)
+    ya, yb, yab = mod(a).float(), mod(b).float(), mod(a + b).float()
+    # a + b is rounded to fp16 before the product; bound that separately
+    scale = float(mod.scales.float().max()) * 8
+    bound = 3 * 2.0 ** -11 * (ya.abs() + yb.abs() + yab.abs()) + 4096 ** 0.5 * 2.0 ** -11 * 4 * scale
+    assert bool(((ya + yb - yab).abs() <= bound).all())
+
+
+def test_error_reporting():
+    layer = synth.make_layer(4, 256, 64, 128).to(DEV)
+    x = synth.make_x(1, 256).to(DEV)
+    with pytest.raises(RuntimeError):
+        ops.gemv(x.cpu(), layer.qweight, layer.qzeros, layer.scales, layer.g_idx, 4, 128)
+    with pytest.raises(ValueError):
+        ops.gemv(x[:, :128].contiguous(), layer.qweight, layer.qzeros, layer.scales, layer.g_idx, 4, 128)
+    with pytest.raises(ValueError):  # 9 rows is not a GEMV
+        ops.gemv(synth.make_x(9, 256).to(DEV), layer.qweight, layer.qzeros, layer.scales, layer.g_idx, 4, 128)
+    with pytest.raises(ValueError):  # 5 bits
+        ops.gemv(x, layer.qweight, layer.qzeros, layer.scales, layer.g_idx, 5, 128)
+    small = torch.zeros(16, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.gemv(synth.make_x(1, 4096).to(DEV), *(lambda L: (L.qweight, L.qzeros, L.scales, L.g_idx))(
+            synth.make_layer(4, 4096, 4096).to(DEV)), 4, 128, workspace=small)
+    with pytest.raises(NotImplementedError):
+        QuantLinear(5, 128, 256, 64, False)
+    with pytest.raises(RuntimeError):
+        QuantLinear(4, 128, 256, 64, False)(torch.zeros(1, 256))
