@@ -81,5 +81,5 @@ def build(force: bool = False, verbose: bool = False, extra_flags=()) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True,
+    print(build(force=("--force" in sys.argv or "--ptxas-v" in sys.argv), verbose=True,
                 extra_flags=("-Xptxas", "-v") if "--ptxas-v" in sys.argv else ()))

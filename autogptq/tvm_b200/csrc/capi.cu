@@ -44,7 +44,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 static int check_layer(int K, int N, int bits, int* group_size) {
     if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return B200GPTQ_ERR_BITS;
     if (K <= 0 || N <= 0 || K % 32 != 0) return B200GPTQ_ERR_SHAPE;
-    if (N % 8 != 0 || (bits == 3 && N % 32 != 0)) return B200GPTQ_ERR_SHAPE;
+    if (N % 32 != 0) return B200GPTQ_ERR_SHAPE;  // qzeros holds N/32*bits words per group
     if (*group_size == -1) *group_size = K;
     if (*group_size <= 0) return B200GPTQ_ERR_SHAPE;
     return B200GPTQ_OK;
@@ -61,7 +61,7 @@ const char* b200gptq_strerror(int status) {
         case B200GPTQ_OK: return "ok";
         case B200GPTQ_ERR_NULL_POINTER: return "a required pointer is NULL";
         case B200GPTQ_ERR_BITS: return "unsupported bit width for this entry point";
-        case B200GPTQ_ERR_SHAPE: return "K, N, M or group_size violate the packing rules (K % 32, N % 8, N % 32 for 3-bit)";
+        case B200GPTQ_ERR_SHAPE: return "K, N, M or group_size violate the packing rules (K % 32 == 0, N % 32 == 0)";
         case B200GPTQ_ERR_ALIGNMENT: return "a device pointer is not 16-byte aligned";
         case B200GPTQ_ERR_WORKSPACE: return "workspace missing or smaller than b200gptq_workspace_bytes()";
         case B200GPTQ_ERR_CUDA: return "CUDA runtime error; see b200gptq_last_cuda_error()";
@@ -121,7 +121,7 @@ int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, 
         return B200GPTQ_ERR_WORKSPACE;
     if (!aligned16(workspace)) return B200GPTQ_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (gemv_stream_supported(M, K, N, bits, group_size))
+    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size))
         return gemv_stream_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
                                     g_idx, x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K,
                                     N, bits, group_size, workspace, st);

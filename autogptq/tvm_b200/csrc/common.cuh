@@ -11,6 +11,13 @@ namespace b200gptq {
 
 constexpr int kRowsPerBlock = 32;  // one "row block": 32 rows of K = bits words of qweight per column
 
+// Scratch layout shared by every kernel: the first kCounterBytes hold arrival counters that
+// are zero between calls (each kernel resets the ones it used); partial sums follow.  Keeping
+// the counter region at a fixed size means no kernel's partial sums ever land on another
+// kernel's counters when the same scratch buffer serves different shapes.
+constexpr size_t kCounterBytes = 16384;
+constexpr int kMaxCounters = (int)(kCounterBytes / sizeof(unsigned int));
+
 __host__ __device__ constexpr int words_per_block(int bits) { return bits; }  // 32 rows * bits / 32
 
 // Thread-local record of the last CUDA runtime error seen by an entry point.

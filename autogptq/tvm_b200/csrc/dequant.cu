@@ -27,8 +27,8 @@ dequant_kernel(const int32_t* __restrict__ qweight, const int32_t* __restrict__ 
     int g_prev = -1;
     __half s[4];
     int z[4];
-#pragma unroll 4
-    for (int j = 0; j < kRowsPerBlock; ++j) {
+#pragma unroll
+    for (int j = 0; j < kRowsPerBlock; ++j) {  // fully unrolled: field positions become constants
         const int k = rb * kRowsPerBlock + j;
         const int g = group_of_row(g_idx, k, group_size);
         if (g != g_prev) {

@@ -68,18 +68,21 @@ gemv_generic_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qw
 
         float s[4], fz[4];
         int g_cur = -1;
-#pragma unroll 4
-        for (int j = 0; j < kRowsPerBlock; ++j) {
-            const int g = uniform ? __shfl_sync(0xffffffffu, g_lane, 0) : __shfl_sync(0xffffffffu, g_lane, j);
-            if (g != g_cur) {  // warp-uniform: g comes from a shuffle
-                g_cur = g;
-                const uint2 sv = __ldg(reinterpret_cast<const uint2*>(scales + (size_t)g * N + n0));
-                const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
-                const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
-                s[0] = s01.x; s[1] = s01.y; s[2] = s23.x; s[3] = s23.y;
-                const int32_t* zrow = qzeros + (size_t)g * zwords;
+        // j is fully unrolled so that every field position is a compile-time constant
 #pragma unroll
-                for (int c = 0; c < 4; ++c) fz[c] = 8388608.f + (float)zero_point<BITS>(zrow, n0 + c);
+        for (int j = 0; j < kRowsPerBlock; ++j) {
+            if (j == 0 || !uniform) {
+                const int g = __shfl_sync(0xffffffffu, g_lane, uniform ? 0 : j);
+                if (g != g_cur) {  // warp-uniform: g comes from a shuffle
+                    g_cur = g;
+                    const uint2 sv = __ldg(reinterpret_cast<const uint2*>(scales + (size_t)g * N + n0));
+                    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
+                    const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
+                    s[0] = s01.x; s[1] = s01.y; s[2] = s23.x; s[3] = s23.y;
+                    const int32_t* zrow = qzeros + (size_t)g * zwords;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) fz[c] = 8388608.f + (float)zero_point<BITS>(zrow, n0 + c);
+                }
             }
             float xf[M];
 #pragma unroll
@@ -163,9 +166,7 @@ int gemv_generic_slices(int K, int N) {
 }
 
 size_t gemv_generic_workspace_bytes(int M, int K, int N) {
-    const int strips = (N + kStripCols - 1) / kStripCols;
-    const size_t counters = ((size_t)strips * sizeof(unsigned int) + 255) / 256 * 256;
-    return counters + (size_t)gemv_generic_slices(K, N) * M * N * sizeof(float);
+    return kCounterBytes + (size_t)gemv_generic_slices(K, N) * M * N * sizeof(float);
 }
 
 template <int BITS, int M>
@@ -176,9 +177,9 @@ static int launch(const __half* x, const int32_t* qweight, const int32_t* qzeros
     const int S = gemv_generic_slices(K, N);
     const int RB = K / kRowsPerBlock;
     const int rbps = (RB + S - 1) / S;
-    const size_t counters = ((size_t)strips * sizeof(unsigned int) + 255) / 256 * 256;
+    if (strips > kMaxCounters) return B200GPTQ_ERR_TOO_LARGE;
     unsigned int* cnt = reinterpret_cast<unsigned int*>(workspace);
-    float* partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + counters);
+    float* partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
     dim3 grid(strips, S);
     gemv_generic_kernel<BITS, M><<<grid, kWarps * 32, 0, stream>>>(
         x, qweight, qzeros, scales, g_idx, x_perm, bias, y, K, N, group_size, rbps, partials, cnt);

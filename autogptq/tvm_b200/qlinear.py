@@ -59,8 +59,8 @@ class QuantLinear(nn.Module):
         super().__init__()
         if bits not in [2, 3, 4, 8]:
             raise NotImplementedError("Only 2,3,4,8 bits are supported.")
-        if infeatures % 32 != 0 or outfeatures % 8 != 0 or (bits == 3 and outfeatures % 32 != 0):
-            raise ValueError("infeatures must be a multiple of 32 and outfeatures of 8 (32 for 3-bit)")
+        if infeatures % 32 != 0 or outfeatures % 32 != 0:
+            raise ValueError("infeatures and outfeatures must be multiples of 32 (the packed format needs it)")
         self.infeatures = infeatures
         self.outfeatures = outfeatures
         self.bits = bits

@@ -198,7 +198,8 @@ def main():
         mods.append(m)
     x_dev = synth.make_x(M, K, seed=rank, device=dev)
     y_dev = torch.empty((P, M, N), dtype=torch.float16, device=dev)
-    ws = ops.get_workspace(dev, 1 << 20)
+    from autogptq.tvm_b200 import _lib
+    ws = ops.get_workspace(dev, _lib.workspace_bytes(_lib.OP_GEMV, M, K, N, bits))
 
     def one_pass():
         for i, m in enumerate(mods):
