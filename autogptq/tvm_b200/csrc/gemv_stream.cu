@@ -27,6 +27,7 @@
 // Reference semantics: auto_gptq/nn_modules/qlinear.py:197-243; the kernel this replaces is
 // the TVM-generated SIMT GEMV src/kernels/gemv_kernel.cu:25-55.
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -82,11 +83,16 @@ template <> struct Traits<4> {
     static constexpr int kBRegs = 4;
     static constexpr int kDepth = 8;   // units in flight per thread
 
-    __device__ static void load(uint4 (&buf)[kVecs], const int32_t* __restrict__ qweight, int N, int kb, int j,
-                                int col, bool active) {
-        if (active) buf[0] = ldg_stream(qweight + (size_t)(4 * kb + j) * N + col);
+    static constexpr int kWordRows = 4;  // word-rows of qweight per unit
+
+    // p points at word-row 4*kb + j of the lane's first column.
+    __device__ static __forceinline__ void load(uint4 (&buf)[kVecs], const int32_t* __restrict__ p, int N,
+                                                bool active) {
+        (void)N;
+        if (active) buf[0] = ldg_stream(p);
         else buf[0] = make_uint4(0, 0, 0, 0);
     }
+    __device__ static __forceinline__ int first_word_row(int kb, int j) { return 4 * kb + j; }
 
     // d[cp] accumulates column pair cp (columns 2cp, 2cp+1 of the lane's 4) over this unit.
     __device__ static void compute(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm, bool has_x,
@@ -125,15 +131,18 @@ template <> struct Traits<3> {
     static constexpr int kBRegs = 20;  // 18 used
     static constexpr int kDepth = 3;
 
-    __device__ static void load(uint4 (&buf)[kVecs], const int32_t* __restrict__ qweight, int N, int kb, int j,
-                                int col, bool active) {
-        const int32_t* p = qweight + (size_t)(3 * (4 * kb + j)) * N + col;
+    static constexpr int kWordRows = 12;
+
+    // p points at word-row 3*(4*kb + j) of the lane's first column.
+    __device__ static __forceinline__ void load(uint4 (&buf)[kVecs], const int32_t* __restrict__ p, int N,
+                                                bool active) {
 #pragma unroll
         for (int r = 0; r < 3; ++r) {
             if (active) buf[r] = ldg_stream(p + (size_t)r * N);
             else buf[r] = make_uint4(0, 0, 0, 0);
         }
     }
+    __device__ static __forceinline__ int first_word_row(int kb, int j) { return 3 * (4 * kb + j); }
 
     // Window t (0..8) of one column's stream (w0, w1, w2); stream offsets -4, 2, 8, 29, 35, 41, 62, 68, 74.
     template <int T_>
@@ -205,6 +214,20 @@ __host__ __device__ inline int unit_owner(int u, int units, int ctas) {
 
 constexpr int kStageGroups = 8;
 
+#ifdef B200GPTQ_TRACE
+__device__ unsigned long long g_trace[1024 * 8];
+__device__ __forceinline__ void trace_mark(int slot) {
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_trace[blockIdx.x * 8 + slot] = t;
+    }
+}
+#define TRACE(slot) trace_mark(slot)
+#else
+#define TRACE(slot)
+#endif
+
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qweight,
@@ -224,6 +247,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     __shared__ float t_x[kStageGroups * kMaxM], t_cx[kStageGroups * kMaxM];
     __shared__ bool is_last;
 
+    TRACE(0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, j = lane & 3;
     const int u_begin = cta_first_unit(blockIdx.x, plan.units, plan.ctas);
@@ -231,16 +255,29 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     const int kbs = plan.kbs;
     const int zwords = N / 32 * BITS;
     const int lane_col = warp * 32 + 4 * g;  // first of the lane's 4 columns inside the column group
+    const size_t unit_stride = (size_t)T::kWordRows * N;
+    const int units_per_group = group_size / UR;
 
-    // ---- start the weight stream before anything else ----
+    // ---- the weight stream: a register ring of D units, refilled as it is consumed ----
+    int pf_cg = u_begin / kbs;
+    int pf_left_cg = kbs - (u_begin - pf_cg * kbs);   // units left in the prefetch column group
+    int pf_left = u_end - u_begin;                    // units left in this CTA's range
+    bool pf_col_ok = pf_cg * kCgCols + lane_col < N;
+    const int32_t* pf_ptr =
+        qweight + (size_t)T::first_word_row(kbs - pf_left_cg, j) * N + (size_t)pf_cg * kCgCols + lane_col;
+    auto prefetch = [&](uint4 (&dst)[T::kVecs]) {
+        T::load(dst, pf_ptr, N, pf_left > 0 && pf_col_ok);
+        pf_ptr += unit_stride;
+        --pf_left;
+        if (--pf_left_cg == 0) {
+            ++pf_cg;
+            pf_left_cg = kbs;
+            pf_col_ok = pf_cg * kCgCols + lane_col < N;
+            pf_ptr = qweight + (size_t)T::first_word_row(0, j) * N + (size_t)pf_cg * kCgCols + lane_col;
+        }
+    };
     uint4 buf[D][T::kVecs];
-#pragma unroll
-    for (int i = 0; i < D; ++i) {
-        const int u = u_begin + i;
-        const int cg = u / kbs, kb = u - cg * kbs;
-        const int col = cg * kCgCols + lane_col;
-        T::load(buf[i], qweight, N, kb, j, col, u < u_end && col < N);
-    }
+
 #pragma unroll
     for (int m = 0; m < kMaxM; ++m) corr_sm[m][tid] = 0.f;
 
@@ -251,7 +288,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
         for (int r = 0; r < 4; ++r) { out[cp][r] = 0.f; d[cp][r] = 0.f; }
 
     bool waited = false;
-    int cur_cg = -1, seg_begin = u_begin, stage_end = -1, stage_kb0 = 0, stage_g0 = 0;
+    int stage_g0 = 0;
 
     // out += scale[group] * d for the lane's 4 columns, then clear d.
     auto flush_group = [&](int grp) {
@@ -271,16 +308,33 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     auto stage = [&](int cg, int kb_a, int kb_b) {
         const int r0 = kb_a * UR, rows = (kb_b - kb_a) * UR;
         const int g0 = r0 / group_size, ng = (r0 + rows - 1) / group_size - g0 + 1;
-        const int n = cg * kCgCols + tid;
+        const int n = min(cg * kCgCols + tid, N - 1);
         // -- static data first: scales and zero-points of this thread's column, gather indices
-        float s_reg[kStageGroups];
-        float z_reg[kStageGroups];
+        int zw, zsh;
+        bool zstr = false;
+        if constexpr (BITS == 3) {
+            const int bit = 3 * (n & 31);
+            zw = 3 * (n >> 5) + (bit >> 5); zsh = bit & 31; zstr = zsh > 29;
+        } else {
+            zw = n >> 3; zsh = 4 * (n & 7);
+        }
+        const __half* sp = scales + (size_t)g0 * N + n;
+        const uint32_t* zp = reinterpret_cast<const uint32_t*>(qzeros) + (size_t)g0 * zwords + zw;
+        float s_reg[kStageGroups], z_reg[kStageGroups];
 #pragma unroll
         for (int gl = 0; gl < kStageGroups; ++gl) {
             s_reg[gl] = 0.f; z_reg[gl] = 0.f;
-            if (gl < ng && n < N) {
-                s_reg[gl] = __half2float(scales[(size_t)(g0 + gl) * N + n]);
-                z_reg[gl] = (float)zero_point<BITS>(qzeros + (size_t)(g0 + gl) * zwords, n);
+            if (gl < ng) {
+                s_reg[gl] = __half2float(__ldg(sp + (size_t)gl * N));
+                const uint32_t lo = __ldg(zp + (size_t)gl * zwords);
+                uint32_t q;
+                if constexpr (BITS == 3) {
+                    const uint32_t hi = zstr ? __ldg(zp + (size_t)gl * zwords + 1) : 0u;
+                    q = __funnelshift_r(lo, hi, zsh) & 7u;
+                } else {
+                    q = (lo >> zsh) & 15u;
+                }
+                z_reg[gl] = __uint_as_float(0x4B000000u | (q + 1u)) - 8388608.f;  // exact small integer
             }
         }
         const bool has_q = tid < rows / 4;
@@ -288,10 +342,14 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
         int4 pidx = make_int4(kq, kq + 1, kq + 2, kq + 3);
         if (has_q && x_perm) pidx = __ldg(reinterpret_cast<const int4*>(x_perm + kq));
         if (!waited) {
+            // The small loads above are already queued; now start the weight stream behind them.
+#pragma unroll
+            for (int i = 0; i < D; ++i) prefetch(buf[i]);
             // x is the only operand a preceding kernel may still be writing
             asm volatile("griddepcontrol.launch_dependents;");
             asm volatile("griddepcontrol.wait;" ::: "memory");
             waited = true;
+            TRACE(1);
         }
         __syncthreads();  // the previous stage's fragments and scales are no longer in use
 #pragma unroll
@@ -300,6 +358,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
             const int kl = 4 * tid;                               // row inside the stage
             const int ul = kl / UR, jl = (kl % UR) / T::kRowsPerLane, f0 = kl % T::kRowsPerLane;
             __half* xh = reinterpret_cast<__half*>(xs);
+#pragma unroll 1
             for (int m = 0; m < M; ++m) {
                 float sx = 0.f, scx = 0.f;
                 if (has_q) {
@@ -338,6 +397,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
             const int m = tid % M, gl = tid / M;
             const int ra = max(r0, (g0 + gl) * group_size), rb = min(r0 + rows, (g0 + gl + 1) * group_size);
             float sx = 0.f, scx = 0.f;
+#pragma unroll 4
             for (int o = (ra - r0) >> 3; o < (rb - r0) >> 3; ++o) {
                 const float2 p = ps[m][o];
                 sx += p.x;
@@ -347,6 +407,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
             t_cx[gl * kMaxM + m] = scx;
         }
         __syncthreads();
+#pragma unroll 1
         for (int m = 0; m < M; ++m) {
             float c = 0.f;
 #pragma unroll
@@ -354,8 +415,8 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
                 if (gl < ng) c = fmaf(s_reg[gl], fmaf(z_reg[gl], t_x[gl * kMaxM + m], t_cx[gl * kMaxM + m]), c);
             corr_sm[m][tid] += c;
         }
-        stage_kb0 = kb_a;
         stage_g0 = g0;
+        TRACE(2);
     };
 
     // Close the segment of column group cg: combine lanes, remove the offset / zero-point term,
@@ -376,6 +437,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
         const int owner_first = unit_owner(cg * kbs, plan.units, plan.ctas);
         const int owner_last = unit_owner(cg * kbs + kbs - 1, plan.units, plan.ctas);
         const bool whole = (owner_first == owner_last);
+#pragma unroll 1
         for (int m = 0; m < M; ++m) {
             float v = corr_sm[m][tid];
             corr_sm[m][tid] = 0.f;
@@ -401,8 +463,10 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
             if (is_last) {
                 __threadfence();
                 if (n < N) {
+#pragma unroll 1
                     for (int m = 0; m < M; ++m) {
                         float v = 0.f;
+#pragma unroll 4
                         for (int i = owner_first; i <= owner_last; ++i)
                             v += __ldcg(partials + ((size_t)(i + cg) * kMaxM + m) * kCgCols + tid);
                         if (bias) v += __half2float(bias[n]);
@@ -413,47 +477,65 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
         }
     };
 
-    for (int base = u_begin; base < u_end; base += D) {
+    // One unit: take slot I of the register ring, refill it with the unit D ahead, multiply.
+    // The ring slot is a compile-time constant, so the switch below enters an unrolled sequence of D
+    // units at the current slot; the heavy, rarely executed stage / finish code exists once.
+    int u = u_begin, slot = 0;
+    int grp = 0, grp_left = 1;       // group of the next unit, units of it still to come
+    const uint32_t* bsm = xs;        // fragments of the next unit for this lane
+    const int bsm_step = M * 4 * T::kBRegs;
+    bool pending = false;            // d holds products that have not been scaled into out yet
+    auto unit = [&](auto slot_c) {
+        constexpr int I = decltype(slot_c)::value;
+        uint4 cur[T::kVecs];
 #pragma unroll
-        for (int i = 0; i < D; ++i) {
-            const int u = base + i;
-            if (u < u_end) {  // uniform over the CTA
-                const int cg = u / kbs, kb = u - cg * kbs;
-                if (cg != cur_cg) {
-                    if (cur_cg >= 0) {
-                        flush_group(((u - 1 - cur_cg * kbs) * UR) / group_size);
-                        finish_segment(cur_cg);
-                    }
-                    cur_cg = cg;
-                    seg_begin = u;
-                    stage_end = -1;
-                } else if ((kb * UR) % group_size == 0 && u != seg_begin) {
-                    flush_group(((kb - 1) * UR) / group_size);
-                }
-                if (u >= stage_end) {
-                    const int su = plan.stage_units;
-                    const int kb_stop = min(min(kbs, (kb / su + 1) * su), kb + (u_end - u));
-                    stage(cg, kb, kb_stop);
-                    stage_end = u + (kb_stop - kb);
-                }
-                uint4 cur[T::kVecs];
-#pragma unroll
-                for (int r = 0; r < T::kVecs; ++r) cur[r] = buf[i][r];
-                {   // refill this slot with the unit D ahead
-                    const int un = u + D;
-                    const int cgn = un / kbs, kbn = un - cgn * kbs;
-                    const int coln = cgn * kCgCols + lane_col;
-                    T::load(buf[i], qweight, N, kbn, j, coln, un < u_end && coln < N);
-                }
-                const uint32_t* bsm = xs + ((size_t)((kb - stage_kb0) * M + g) * 4 + j) * T::kBRegs;
-                T::compute(cur, bsm, g < M, d);
+        for (int r = 0; r < T::kVecs; ++r) cur[r] = buf[I][r];
+        prefetch(buf[I]);
+        T::compute(cur, bsm, g < M, d);
+        bsm += bsm_step;
+        ++u;
+        pending = true;
+        if (--grp_left == 0) {
+            flush_group(grp);
+            ++grp;
+            grp_left = units_per_group;
+            pending = false;
+        }
+    };
+
+    while (u < u_end) {
+        const int cg = u / kbs;
+        const int kb = u - cg * kbs;
+        // stage as far as the stage grid, the column group and this CTA's range allow
+        const int su = plan.stage_units;
+        const int kb_stop = min(min(kbs, (kb / su + 1) * su), kb + (u_end - u));
+        stage(cg, kb, kb_stop);
+        grp = (kb * UR) / group_size;
+        grp_left = units_per_group - (kb - grp * units_per_group);
+        bsm = xs + (size_t)(g * 4 + j) * T::kBRegs;
+        const int run_end = u + (kb_stop - kb);
+        while (u < run_end) {
+            switch (slot) {
+#define B200GPTQ_UNIT(I)                                             \
+    case I:                                                          \
+        if constexpr (I < D) {                                       \
+            unit(std::integral_constant<int, I>{});                  \
+            if (u == run_end) { slot = (I + 1) % D; break; }         \
+        }
+                B200GPTQ_UNIT(0) B200GPTQ_UNIT(1) B200GPTQ_UNIT(2) B200GPTQ_UNIT(3)
+                B200GPTQ_UNIT(4) B200GPTQ_UNIT(5) B200GPTQ_UNIT(6) B200GPTQ_UNIT(7)
+#undef B200GPTQ_UNIT
+                default: slot = 0;
             }
         }
+        TRACE(3);
+        // the segment ends here if the next unit belongs to another column group or to another CTA
+        if (u == u_end || kb_stop == kbs) {
+            if (pending) { flush_group(grp); pending = false; }
+            finish_segment(cg);
+        }
     }
-    if (cur_cg >= 0) {
-        flush_group(((u_end - 1 - cur_cg * kbs) * UR) / group_size);
-        finish_segment(cur_cg);
-    }
+    TRACE(4);
 }
 
 int ctas_per_sm() {
@@ -515,6 +597,12 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
 }
 
 }  // namespace
+
+#ifdef B200GPTQ_TRACE
+extern "C" __attribute__((visibility("default"))) int b200gptq_trace_read(unsigned long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n);
+}
+#endif
 
 // The streaming kernel handles groups k / group_size only (no g_idx), whole units per group, and
 // x rows that can be read 8 bytes at a time.
