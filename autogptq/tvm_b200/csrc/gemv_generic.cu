@@ -177,7 +177,7 @@ static int launch(const __half* x, const int32_t* qweight, const int32_t* qzeros
     const int S = gemv_generic_slices(K, N);
     const int RB = K / kRowsPerBlock;
     const int rbps = (RB + S - 1) / S;
-    if (strips > kMaxCounters) return B200GPTQ_ERR_TOO_LARGE;
+    if (strips >= kMaxCounters - 1) return B200GPTQ_ERR_TOO_LARGE;  // the last counter word is reserved
     unsigned int* cnt = reinterpret_cast<unsigned int*>(workspace);
     float* partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
     dim3 grid(strips, S);

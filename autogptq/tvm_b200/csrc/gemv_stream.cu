@@ -577,7 +577,7 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
                   const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int group_size,
                   void* workspace, cudaStream_t stream) {
     const Plan plan = make_plan(K, N, BITS, group_size);
-    if (plan.cgs > kMaxCounters) return B200GPTQ_ERR_TOO_LARGE;
+    if (plan.cgs >= kMaxCounters - 1) return B200GPTQ_ERR_TOO_LARGE;  // the last counter word is reserved
     unsigned int* counters = reinterpret_cast<unsigned int*>(workspace);
     float* partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
 

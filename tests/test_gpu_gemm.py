@@ -1,0 +1,103 @@
+"""GPU parity of the tcgen05 prefill dequant-GEMM against the CPU oracle (through the C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gptq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from autogptq.tvm_b200 import QuantLinear, ops, synth
+    DEV = torch.device("cuda:0")
+
+
+def _layer_np(layer):
+    return (layer.qweight.numpy(), layer.qzeros.numpy(), layer.scales.numpy(), layer.g_idx.numpy())
+
+
+def _check(y, x, W, bias=None):
+    ref = O.forward_fp64(x, W, bias)
+    got = y.detach().cpu().numpy().astype(np.float64)
+    err = np.abs(got - ref)
+    tol = O.output_tolerance(x, W)              # contract: 1e-2 * ||x||_2 * max|w| per output
+    assert np.all(err <= tol), f"contract tolerance exceeded: {err.max()} > {tol.min()}"
+    band = 2.0 ** -10 * np.abs(ref) + 0.02 * tol  # fp32 accumulation, one fp16 rounding
+    assert np.all(err <= band), f"max err {err.max()} outside the fp32-accumulate band"
+
+
+def _status_clear():
+    ws = ops.get_workspace(DEV, 1 << 20)
+    torch.cuda.synchronize()
+    assert int(ws[:16384].view(torch.int32)[-1]) == 0, "a bounded wait of the GEMM kernel expired"
+
+
+GEMM_CASES = [
+    # bits, K, N, gs, M, bias
+    (4, 256, 128, 128, 16, False),
+    (4, 512, 256, 128, 48, True),
+    (4, 1024, 384, 64, 130, False),      # two M tiles per CTA, M tail
+    (4, 352, 96, 32, 20, False),         # K tail (352 = 5.5 k-tiles), N < one tile
+    (4, 4096, 1024, 128, 300, True),
+    (3, 256, 128, 128, 16, False),
+    (3, 1024, 256, 128, 77, True),
+    (3, 4096, 512, 128, 200, False),
+    (3, 352, 96, -1, 33, False),
+    (4, 512, 128, 128, 1, False),        # works for any M >= 1
+]
+
+
+@pytest.mark.parametrize("bits,K,N,gs,M,bias", GEMM_CASES)
+def test_gemm_vs_oracle(bits, K, N, gs, M, bias):
+    layer = synth.make_layer(bits, K, N, gs, False, bias=bias, seed=K + N + M)
+    x = synth.make_x(M, K, seed=M)
+    _, _, W = O.dequantize(*_layer_np(layer), bits)
+    d = layer.to(DEV)
+    y = ops.gemm(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias)
+    _check(y, x.numpy(), W, None if layer.bias is None else layer.bias.numpy())
+    y2 = ops.gemm(x.to(DEV), d.qweight, d.qzeros, d.scales, d.g_idx, bits, gs, bias=d.bias)
+    assert torch.equal(y, y2), "explicit k // group_size g_idx must give the same bits"
+    _status_clear()
+
+
+@pytest.mark.parametrize("bits,K,N,gs,M", [(4, 1024, 256, 128, 40), (3, 1024, 256, 128, 150), (4, 512, 160, 64, 17)])
+def test_gemm_act_order_through_quantlinear(bits, K, N, gs, M):
+    layer = synth.make_layer(bits, K, N, gs, act_order=True, seed=3 * bits + M)
+    _, _, W = O.dequantize(*_layer_np(layer), bits)
+    mod = QuantLinear(bits, gs, K, N, False)
+    mod.qweight, mod.qzeros, mod.scales, mod.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
+    mod = mod.to(DEV)
+    x = synth.make_x(M, K, seed=5)
+    y = mod(x.to(DEV).reshape(1, M, K))
+    assert tuple(y.shape) == (1, M, N)
+    _check(y.reshape(M, N), x.numpy(), W)
+    _status_clear()
+
+
+@pytest.mark.parametrize("M", [16, 128])
+def test_gemm_config2_vs_oracle(M):
+    """4-bit, K=4096, N=12288 (fused QKV), the prefill configuration, at the sizes the oracle finishes quickly."""
+    layer = synth.make_layer(4, 4096, 12288, 128, False, seed=21)
+    x = synth.make_x(M, 4096, seed=M)
+    _, _, W = O.dequantize(*_layer_np(layer), 4)
+    d = layer.to(DEV)
+    y = ops.gemm(x.to(DEV), d.qweight, d.qzeros, d.scales, None, 4, 128)
+    _check(y, x.numpy(), W)
+    _status_clear()
+
+
+@pytest.mark.parametrize("bits,M", [(4, 2048), (4, 512), (3, 512)])
+def test_gemm_full_size_against_dequantised_product(bits, M):
+    """At the full prefill sizes the check is a property: the fused kernel equals x @ W for the W that the
+    (bit-exact, separately tested) dequantise kernel produces, evaluated by torch in fp32."""
+    K, N = 4096, 12288
+    d = synth.make_layer(bits, K, N, 128, False, seed=33, device=DEV)
+    x = synth.make_x(M, K, seed=9, device=DEV)
+    _, W = ops.dequantize(d.qweight, d.qzeros, d.scales, d.g_idx, bits, 128, want_q=False)
+    y = ops.gemm(x, d.qweight, d.qzeros, d.scales, None, bits, 128)
+    ref = x.float() @ W.float()
+    err = (y.float() - ref).abs()
+    tol = 1e-2 * x.float().norm(dim=1, keepdim=True) * W.float().abs().max()
+    assert bool((err <= tol).all())
+    assert bool((err <= 2.0 ** -10 * ref.abs() + 0.02 * tol).all())
+    _status_clear()
