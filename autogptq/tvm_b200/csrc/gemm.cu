@@ -2,15 +2,20 @@
 //
 //   y[M, N] = x[M, K] @ W[K, N] (+ bias),   W[k, n] = scales[g, n] * (q[k, n] - zero[g, n])
 //
-// One CTA computes a (128*MT) x 128 tile of y.  Roles of its six warps:
-//   warp 0      TMA producer: x tiles (128 rows x 64 k, 128-byte swizzle) into the stage ring
-//               and the matching packed weight rows (plain 2-D tile) into the same stage
-//   warps 1..4  weight producers: each thread owns one of the 128 columns, reads that column's
-//               packed words from the stage, dequantises them to the exact fp16
-//               value of the reference (auto_gptq/nn_modules/qlinear.py:242: one rounding) and
-//               writes 128-byte-swizzled K-major rows of the B operand; afterwards the same
-//               warps run the epilogue (tcgen05.ld -> fp16 -> global)
-//   warp 5      allocates tensor memory and issues tcgen05.mma (M=128, N=128, K=16, f16 -> f32)
+// The product is computed transposed, y^T = W^T x^T, so that the dequantised weights are the
+// A operand of tcgen05.mma and can live in TENSOR MEMORY: they never touch shared memory, which
+// on this part is the resource a mixed-input GEMM runs out of first (an MMA whose operands both
+// come from shared memory already consumes its whole read bandwidth at 128 x 128 tiles).
+// One CTA computes 128 output columns for a tile of TN <= 256 rows of x:
+//   warp 0      TMA producer: per k-tile (64 rows of K) an x tile (TN rows x 64 k, 128-byte
+//               swizzle) and the packed weight rows of the CTA's 128 columns, into a stage ring
+//   warps 1..16 weight producers in two groups that take k-tiles in turn: each thread owns one of the 128 columns and one 32-row block of
+//               the k-tile; it reads its packed words from the stage, dequantises them to the
+//               exact fp16 value of the reference (auto_gptq/nn_modules/qlinear.py:242: one
+//               rounding) and stores 16 registers into the A buffer of that stage in tensor memory
+//               (tcgen05.st); afterwards the same warps run the epilogue (tcgen05.ld -> fp16 -> y)
+//   warp 17     allocates tensor memory and issues tcgen05.mma (M = 128 columns, N = TN rows of x,
+//               K = 16, f16 x f16 -> f32 accumulators in tensor memory columns 0..TN-1)
 // Stages hand over through mbarriers; tcgen05.commit releases a stage when its MMAs retire.
 // Every wait is bounded: on expiry the kernel raises a sticky status word, unwinds, frees its
 // tensor memory and returns.
@@ -29,20 +34,20 @@ namespace b200gptq {
 
 namespace {
 
-constexpr int BN = 128, BK = 64, BM = 128;
-constexpr int kGemmThreads = 192;
-constexpr int kATileBytes = BM * BK * 2;  // 16 KB
-constexpr int kBTileBytes = BN * BK * 2;  // 16 KB
+constexpr int BN = 128;                 // output columns per CTA = rows of the MMA's A operand
+constexpr int BK = 64;                  // rows of K per stage
+constexpr int kMaxTN = 256;             // rows of x per CTA = N of the MMA
+constexpr int kWeightWarps = 8;         // warps that build one k-tile's A operand
+constexpr int kWeightGroups = 2;        // groups of such warps, taking k-tiles in turn
+constexpr int kMmaWarp = 1 + kWeightWarps * kWeightGroups;
+constexpr int kGemmThreads = 32 * (2 + kWeightWarps * kWeightGroups);  // TMA warp, weight warps, MMA warp
+constexpr int kPackedTileBytes = 4096;  // up to 8 word-rows x 128 columns of packed weights per k-tile
+constexpr int kMaxStages = 8;
+constexpr int kTmemCols = 512;          // accumulators in columns [0, 256), A buffers in [256, 512)
+constexpr int kTmemAOffset = 256;
+constexpr int kTmemAColsPerStage = 32;  // 64 k x fp16 = 32 columns of 32 bits
+constexpr int kSmemBudget = 222 * 1024;  // ring bytes; the opt-in maximum per CTA is 227 KB
 constexpr int kStatusWord = kMaxCounters - 1;  // sticky error word inside the counter region
-
-constexpr int kPackedTileBytes = 4096;     // up to 8 word-rows x 128 columns of packed weights per k-tile
-
-template <int MT> struct GemmCfg {
-    static constexpr int kStages = MT == 1 ? 5 : 4;
-    static constexpr int kStageBytes = MT * kATileBytes + kBTileBytes + kPackedTileBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static constexpr int kTmemCols = MT * BN;  // 128 or 256: powers of two
-};
 
 // 3-bit: order in which the 32 fields of a row block leave the 7-window unpack (pairs are
 // adjacent entries).  x is permuted the same way by the pre-pass.
@@ -86,27 +91,32 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint4 (&v)[4]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z),
+          "r"(v[1].w), "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z),
+          "r"(v[3].w) : "memory");
+}
+// A operand in tensor memory, B operand described in shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 
 // K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -203,49 +213,49 @@ prep_x_kernel(const __half* __restrict__ x, const int32_t* __restrict__ x_perm, 
     }
 }
 
-template <int BITS, int MT>
+template <int BITS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
             const int32_t* __restrict__ g_idx, const __half* __restrict__ bias, __half* __restrict__ y, int M, int K,
-            int N, int group_size, unsigned int* __restrict__ status) {
-    using Cfg = GemmCfg<MT>;
-    constexpr int S = Cfg::kStages;
+            int N, int group_size, int TN, int S, unsigned int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;            // operand tiles need 1024-byte alignment
+    const uint32_t base = (raw + 1023u) & ~1023u;            // swizzled tiles need 1024-byte alignment
     uint8_t* base_ptr = smem_raw + (base - raw);
-    const uint32_t bar_base = base + S * Cfg::kStageBytes;   // tma_full[S], b_full[S], empty[S], accum
+    __shared__ __align__(8) uint64_t bars[3 * kMaxStages + 1];  // tma[S], a_full[S], empty[S], accum
     __shared__ uint32_t tmem_base_holder;
     __shared__ volatile int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.y * BN, m0 = blockIdx.x * (BM * MT);
+    const int n0 = blockIdx.y * BN, m0 = blockIdx.x * TN;
     const int KT = (K + BK - 1) / BK;
+    const uint32_t x_tile_bytes = (uint32_t)TN * BK * 2;
+    const uint32_t stage_bytes = x_tile_bytes + kPackedTileBytes;
 
-    auto tma_bar = [&](int s) { return bar_base + 8u * s; };          // x tiles + packed weights have landed
-    auto full_bar = [&](int s) { return bar_base + 8u * (S + s); };    // the B operand has been written
-    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
-    const uint32_t accum_bar = bar_base + 8u * (3 * S);
-    auto a_tile = [&](int s, int mt) { return base + s * Cfg::kStageBytes + mt * kATileBytes; };
-    auto b_tile = [&](int s) { return base + s * Cfg::kStageBytes + MT * kATileBytes; };
-    auto p_tile = [&](int s) { return base + s * Cfg::kStageBytes + MT * kATileBytes + kBTileBytes; };
+    const uint32_t bar_base = smem_u32(bars);
+    auto tma_bar = [&](int s) { return bar_base + 8u * s; };                      // x tile + packed weights landed
+    auto full_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };      // A operand stored in tensor memory
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + s); }; // the stage's MMAs have retired
+    const uint32_t accum_bar = bar_base + 8u * (3 * kMaxStages);
+    auto x_tile = [&](int s) { return base + s * stage_bytes; };
+    auto p_tile = [&](int s) { return base + s * stage_bytes + x_tile_bytes; };
     constexpr int kWordRowsPerTile = 2 * Dequant<BITS>::kWords;     // word-rows of qweight per 64 rows of K
     constexpr uint32_t kPackedBytes = kWordRowsPerTile * BN * 4;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < S; ++s) {
-            mbar_init(tma_bar(s), 1);    // the TMA producer's expect_tx arrive
-            mbar_init(full_bar(s), 4);   // one arrive per weight warp
-            mbar_init(empty_bar(s), 1);  // tcgen05.commit
+            mbar_init(tma_bar(s), 1);               // the TMA producer's expect_tx arrive
+            mbar_init(full_bar(s), kWeightWarps);   // one arrive per weight warp
+            mbar_init(empty_bar(s), 1);             // tcgen05.commit
         }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_holder)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+                     ::"r"(smem_u32(&tmem_base_holder)), "r"((uint32_t)kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -256,138 +266,126 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     if (warp == 0) {
         // ===== TMA producer =====
         if (lane == 0) {
+            int s = 0, round = 0;
             for (int kt = 0; kt < KT; ++kt) {
-                const int s = kt % S, round = kt / S;
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, &abort_flag)) break;
-                mbar_arrive_expect_tx(tma_bar(s), MT * kATileBytes + kPackedBytes);
+                mbar_arrive_expect_tx(tma_bar(s), x_tile_bytes + kPackedBytes);
                 tma_load_2d(p_tile(s), &tmap_w, n0, kt * kWordRowsPerTile, tma_bar(s));
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-                    tma_load_2d(a_tile(s, mt), &tmap_x, kt * BK, m0 + mt * BM, tma_bar(s));
+                tma_load_2d(x_tile(s), &tmap_x, kt * BK, m0, tma_bar(s));
+                if (++s == S) { s = 0; ++round; }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ===== MMA issuer =====
         if (lane == 0) {
-            constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
             bool ok = true;
-            for (int kt = 0; kt < KT && ok; ++kt) {
-                const int s = kt % S, round = kt / S;
+            int s = 0, round = 0;
+            for (int kt = 0; kt < KT; ++kt) {
                 ok = mbar_wait(tma_bar(s), round & 1, &abort_flag) && mbar_wait(full_bar(s), round & 1, &abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t bdesc = make_smem_desc(b_tile(s));
+                const uint64_t bdesc = make_smem_desc(x_tile(s));
+                const uint32_t a_addr = tmem_base + kTmemAOffset + kTmemAColsPerStage * s;
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const uint64_t adesc = make_smem_desc(a_tile(s, mt));
-#pragma unroll
-                    for (int k16 = 0; k16 < BK / 16; ++k16)
-                        umma_f16(tmem_base + mt * BN, adesc + 2u * k16, bdesc + 2u * k16, idesc,
-                                 (kt > 0 || k16 > 0) ? 1u : 0u);
-                }
+                for (int k16 = 0; k16 < BK / 16; ++k16)
+                    umma_f16_ts(tmem_base, a_addr + 8u * k16, bdesc + 2u * k16, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
                 umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+                if (++s == S) { s = 0; ++round; }
             }
             if (ok) umma_commit(accum_bar);
         }
     } else {
-        // ===== weight producers (128 threads, one column each), then epilogue =====
-        const int t = threadIdx.x - 32;     // 0..127
-        const int n = n0 + t;
+        // ===== weight producers (256 threads: one column x one 32-row block each), then epilogue =====
+        const int quarter = warp & 3;                 // tensor-memory lanes 32*quarter .. +31 belong to this warp
+        const int wgroup = (warp - 1) / kWeightWarps; // this group takes k-tiles wgroup, wgroup + kWeightGroups, ...
+        const int kh = ((warp - 1) % kWeightWarps) >> 2;  // which 32-row block of the 64-row k-tile
+        const int col = 32 * quarter + lane;          // column inside the tile = tensor-memory lane
+        const int n = n0 + col;
         const bool col_ok = n < N;
-        const int wt = t >> 5;              // weight warp 0..3
         constexpr int W = Dequant<BITS>::kWords;
         const int zwords = N / 32 * BITS;
         const int RB = K / 32;
-        const uint32_t row_off = (uint32_t)(t >> 3) * 1024u + (uint32_t)(t & 7) * 128u;
-        int g_cur = -1;
-        __half s_cur = __float2half(0.f);
-        int z_cur = 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * quarter) << 16);
+
+        // group parameters of the row block this thread handles in the current and the next k-tile
+        auto group_of = [&](int rb) { return g_idx ? __ldg(g_idx + 32 * rb) : (32 * rb) / group_size; };
+        auto load_group = [&](int rb, int& g, __half& sc, int& z) {
+            if (col_ok && rb < RB) {
+                g = group_of(rb);
+                sc = scales[(size_t)g * N + n];
+                z = zero_point<BITS>(qzeros + (size_t)g * zwords, n);
+            }
+        };
+        int g_cur = -1, g_nxt = -1, z_cur = 0, z_nxt = 0;
+        __half s_cur = __float2half(0.f), s_nxt = __float2half(0.f);
+        load_group(2 * wgroup + kh, g_cur, s_cur, z_cur);
 
         bool ok = true;
-        for (int kt = 0; kt < KT; ++kt) {
-            const int s = kt % S, round = kt / S;
-            // the stage is free (its previous MMAs retired) before the TMA refilled it, so waiting for
-            // the refill also orders this thread's B writes after those MMAs
-            ok = mbar_wait(tma_bar(s), round & 1, &abort_flag);
-            if (!ok) break;
-            const uint32_t* pw = reinterpret_cast<const uint32_t*>(base_ptr + (p_tile(s) - base)) + t;
-            uint32_t cur[2][W];
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int r = 0; r < W; ++r) cur[h][r] = pw[(h * W + r) * BN];
-            uint8_t* brow = base_ptr + (b_tile(s) - base) + row_off;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int rb = 2 * kt + h;
-                uint4 out[4];
-                if (col_ok && rb < RB) {
-                    const int g = g_idx ? __ldg(g_idx + 32 * rb) : (32 * rb) / group_size;
-                    if (g != g_cur) {
-                        g_cur = g;
-                        s_cur = scales[(size_t)g * N + n];
-                        z_cur = zero_point<BITS>(qzeros + (size_t)g * zwords, n);
-                    }
-                    Dequant<BITS>::run(cur[h], s_cur, z_cur, out);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
-                }
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int chunk = 4 * h + c;
-                    *reinterpret_cast<uint4*>(brow + (((uint32_t)chunk ^ (uint32_t)(t & 7)) << 4)) = out[c];
-                }
+        int s = wgroup % S, round = wgroup / S;
+        for (int kt = wgroup; kt < KT; kt += kWeightGroups) {
+            const int rb = 2 * kt + kh;
+            // fetch the scale / zero-point of this thread's next k-tile now, a whole iteration ahead of their use
+            constexpr int kRbStep = 2 * kWeightGroups;
+            if (rb + kRbStep < RB && col_ok) {
+                const int gn = group_of(rb + kRbStep);
+                if (gn != g_cur) load_group(rb + kRbStep, g_nxt, s_nxt, z_nxt);
+                else { g_nxt = g_cur; s_nxt = s_cur; z_nxt = z_cur; }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor core reads
+            // The TMA refilled this stage only after its previous MMAs retired (empty barrier), so the
+            // A buffer of the stage in tensor memory is free as well.
+            ok = mbar_wait(tma_bar(s), round & 1, &abort_flag);
+            ok = __all_sync(0xffffffffu, ok);   // the tensor-memory store below is warp-collective
+            if (!ok) break;
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(base_ptr + (p_tile(s) - base)) + col;
+            uint32_t cur[W];
+#pragma unroll
+            for (int r = 0; r < W; ++r) cur[r] = pw[(kh * W + r) * BN];
+            uint4 out[4];
+            if (col_ok && rb < RB) {
+                Dequant<BITS>::run(cur, s_cur, z_cur, out);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
+            }
+            tmem_st16(lane_addr + kTmemAOffset + kTmemAColsPerStage * s + 16 * kh, out);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(full_bar(s));
+            g_cur = g_nxt; s_cur = s_nxt; z_cur = z_nxt;
+            s += kWeightGroups;
+            while (s >= S) { s -= S; ++round; }
         }
 
-        // ----- epilogue: TMEM -> registers -> fp16 -> global -----
+        // ----- epilogue: accumulators (lane = output column, column = row of x) -> fp16 -> y -----
         if (ok) ok = mbar_wait(accum_bar, 0, &abort_flag);
         ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+            const float b = (bias && col_ok) ? __half2float(bias[n]) : 0.f;
 #pragma unroll 1
-            for (int mt = 0; mt < MT; ++mt) {
-                const int m = m0 + mt * BM + quarter * 32 + lane;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + c * 32), r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    const int nc = n0 + c * 32;
-                    if (m < M && nc < N) {
-                        __half* dst = y + (size_t)m * N + nc;
+            // the warps that share a lane quarter take the 16-row chunks in turn
+            for (int c = (warp - 1) >> 2; c < TN / 16; c += kWeightWarps * kWeightGroups / 4) {
+                uint32_t r[16];
+                tmem_ld16(lane_addr + 16u * c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int m = m0 + 16 * c;
+                if (col_ok) {
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t o[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                float f0 = __uint_as_float(r[8 * q + 2 * e]), f1 = __uint_as_float(r[8 * q + 2 * e + 1]);
-                                if (bias) {
-                                    f0 += __half2float(bias[nc + 8 * q + 2 * e]);
-                                    f1 += __half2float(bias[nc + 8 * q + 2 * e + 1]);
-                                }
-                                o[e] = h2_as_u32(__floats2half2_rn(f0, f1));
-                            }
-                            *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(o[0], o[1], o[2], o[3]);
-                        }
-                    }
+                    for (int i = 0; i < 16; ++i)
+                        if (m + i < M) y[(size_t)(m + i) * N + n] = __float2half_rn(__uint_as_float(r[i]) + b);
                 }
             }
         }
-        (void)wt;
     }
 
     // ----- teardown: every role arrives here, also after a timed-out wait -----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (threadIdx.x == 0 && abort_flag) atomicExch(status + kStatusWord, 1u);
-    if (warp == 5) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
     }
 }
 
@@ -408,43 +406,59 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-template <int BITS, int MT>
+int pick_tn(int M) {
+    if (M <= 16) return 16;
+    if (M <= 32) return 32;
+    if (M <= 64) return 64;
+    if (M <= 128) return 128;
+    return kMaxTN;
+}
+
+template <int BITS>
 int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                 const int32_t* g_idx, const __half* bias, __half* y, int M, int K, int N, int group_size,
                 unsigned int* status, cudaStream_t stream) {
-    using Cfg = GemmCfg<MT>;
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) { set_last_cuda_error((int)cudaErrorNotSupported); return B200GPTQ_ERR_CUDA; }
-    CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
-    const cuuint32_t box[2] = {BK, BM};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x_for_tma), dims, strides,
-                              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
-    // packed weights: int32 [K/32*bits, N], a box of (word-rows of one k-tile) x 128 columns, no swizzle
-    CUtensorMap tmap_w;
-    const cuuint64_t wdims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 32 * BITS)};
-    const cuuint64_t wstrides[1] = {(cuuint64_t)N * sizeof(int32_t)};
-    const cuuint32_t wbox[2] = {BN, 2 * Dequant<BITS>::kWords};
-    const CUresult rw = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t*>(qweight), wdims, wstrides,
-                               wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rw != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
+    const int TN = pick_tn(M);
+    const int stage_bytes = TN * BK * 2 + kPackedTileBytes;
+    int S = kSmemBudget / stage_bytes;
+    if (S > kMaxStages) S = kMaxStages;
+    const int smem_bytes = S * stage_bytes + 1024;  // + slack to align the ring to 1024 bytes
 
-    static bool attr_set[64][2][2] = {};
+    CUtensorMap tmap_x, tmap_w;
+    const cuuint32_t estr[2] = {1, 1};
+    {   // x: fp16 [M, K]; a box is 64 k x TN rows, 128-byte swizzle, rows beyond M read as zero
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+        const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
+        const cuuint32_t box[2] = {BK, (cuuint32_t)TN};
+        const CUresult r = encode(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x_for_tma), dims,
+                                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
+    }
+    {   // packed weights: int32 [K/32*bits, N]; a box is the word-rows of one k-tile x 128 columns
+        const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 32 * BITS)};
+        const cuuint64_t strides[1] = {(cuuint64_t)N * sizeof(int32_t)};
+        const cuuint32_t box[2] = {BN, 2 * Dequant<BITS>::kWords};
+        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t*>(qweight), dims,
+                                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
+    }
+
+    static bool attr_set[64][2] = {};
     int dev = 0;
     B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
-    auto kernel = gemm_kernel<BITS, MT>;
-    if (dev >= 0 && dev < 64 && !attr_set[dev][BITS == 4][MT - 1]) {
-        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set[dev][BITS == 4][MT - 1] = true;
+    auto kernel = gemm_kernel<BITS>;
+    if (dev >= 0 && dev < 64 && !attr_set[dev][BITS == 4]) {
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               226 * 1024));
+        attr_set[dev][BITS == 4] = true;
     }
-    dim3 grid((M + BM * MT - 1) / (BM * MT), (N + BN - 1) / BN);
-    kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmap, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N,
-                                                           group_size, status);
+    dim3 grid((M + TN - 1) / TN, (N + BN - 1) / BN);
+    kernel<<<grid, kGemmThreads, smem_bytes, stream>>>(tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N,
+                                                     group_size, TN, S, status);
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
 }
@@ -474,13 +488,8 @@ int gemm_dispatch(const __half* x, const int32_t* qweight, const int32_t* qzeros
         B200GPTQ_CUDA_TRY(cudaGetLastError());
         xt = xp;
     }
-    const bool two = M > BM;
-    if (bits == 4)
-        return two ? launch_gemm<4, 2>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream)
-                   : launch_gemm<4, 1>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream);
-    if (bits == 3)
-        return two ? launch_gemm<3, 2>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream)
-                   : launch_gemm<3, 1>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream);
+    if (bits == 4) return launch_gemm<4>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream);
+    if (bits == 3) return launch_gemm<3>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream);
     return B200GPTQ_ERR_BITS;
 }
 
