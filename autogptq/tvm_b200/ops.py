@@ -135,3 +135,30 @@ def gemm(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=Non
     """Prefill dequant-GEMM on tcgen05, ``x`` fp16 ``[M, K]`` -> fp16 ``[M, N]``."""
     return _matmul("b200gptq_gemm", _lib.OP_GEMM, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits,
                    group_size, out, workspace)
+
+
+def gemv_static(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None, out=None):
+    """Decode GEMV through ``b200gptq_gemv_static``: same results as :func:`gemv`, but the kernels'
+    scratch is the fixed array inside the library, so nothing is allocated for the call except (when
+    ``out`` is not given) the result tensor.  Meant for hosts that cannot allocate device memory at
+    launch time; calls on one device must be ordered on a stream because they share that array."""
+    _need_cuda("x", x, torch.float16)
+    _need_cuda("qweight", qweight, torch.int32)
+    _need_cuda("qzeros", qzeros, torch.int32)
+    _need_cuda("scales", scales, torch.float16)
+    for name, t, dt in (("g_idx", g_idx, torch.int32), ("x_perm", x_perm, torch.int32), ("bias", bias, torch.float16)):
+        if t is not None:
+            _need_cuda(name, t, dt)
+    K, N = layer_dims(qweight, bits)
+    if x.dim() != 2 or x.shape[1] != K:
+        raise ValueError(f"x must be [M, {K}], got {tuple(x.shape)}")
+    M = x.shape[0]
+    dev = x.device
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        st = _lib.lib.b200gptq_gemv_static(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
+                                           _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
+                                           _stream(dev))
+    _lib.check(st, "b200gptq_gemv_static")
+    return out

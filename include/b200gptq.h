@@ -129,6 +129,31 @@ B200GPTQ_API int b200gptq_sort_rows(const int32_t* qweight, const int32_t* g_idx
                        int K, int N, int bits,
                        int32_t* qweight_sorted, int32_t* g_idx_sorted, void* stream);
 
+/*
+ * Decode GEMV without caller scratch (no counterpart in the reference; the reference's kernels
+ * need no scratch because they never split K across thread blocks).
+ *
+ * Same arithmetic, arguments and results as b200gptq_gemv, for hosts that cannot allocate
+ * device memory where they launch: plugins called from inside another runtime, engines whose
+ * memory plan is frozen, loops in which cudaMalloc is forbidden.  The partial sums and arrival
+ * counters live in a fixed array of b200gptq_gemv_static_capacity() bytes (4 MiB) inside the
+ * library's device image; each GPU that loads the library holds that memory until its context
+ * ends.  The call never allocates or frees memory.
+ *
+ *  - Problems with b200gptq_workspace_bytes(B200GPTQ_OP_GEMV, ...) above the capacity return
+ *    B200GPTQ_ERR_TOO_LARGE.
+ *  - All calls on one device share the array: calls that may overlap on the GPU race with each
+ *    other; order them on one stream (or with events).
+ *  - The first call on a device looks the array up and zero-fills its counters with synchronous
+ *    runtime calls; make that call before any stream capture begins.
+ */
+B200GPTQ_API int b200gptq_gemv_static(const void* x, const int32_t* qweight, const int32_t* qzeros,
+                         const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,
+                         void* y, int M, int K, int N, int bits, int group_size, void* stream);
+
+/* Bytes of the built-in scratch array used by b200gptq_gemv_static (per device). */
+B200GPTQ_API size_t b200gptq_gemv_static_capacity(void);
+
 #ifdef __cplusplus
 }
 #endif
