@@ -3,31 +3,35 @@
 //   y[m, n] = sum_k x[m, xk(k)] * scales[g, n] * (q[k, n] - zero[g, n]),   g = k / group_size
 //
 // The kernel is bound by HBM bandwidth and, on B200, almost by instruction issue as well
-// (about two instructions per weight are available at full bandwidth), so the inner loop
-// is built to spend roughly one instruction per weight:
+// (about two instructions per weight are available at full bandwidth), and a single layer lasts
+// only a few microseconds, so three things shape it:
 //
-//  * weights go from global memory straight to registers with 128-bit loads, several
-//    units ahead of their use (no shared-memory staging, no barriers on the weight path);
-//  * fields are never shifted into place or converted: a LOP3 masks two fields of a word
-//    and ORs in an fp16 exponent, which yields the half2 (c_lo + q_lo, c_hi + q_hi) with
-//    small known offsets c (8..128);
-//  * the products are done by mma.sync m16n8k16 (f16 x f16 -> f32): the 16 rows of the A
-//    tile are 16 output columns, the 8 columns of B are the (up to 8) rows of x, so one
-//    instruction retires 256 weights of a warp for every M <= 8;
-//  * the offsets and zero-points are removed afterwards: per group, sum_k (c_k + q_k) x_k is
-//    scaled by s, and  sum_g s * (sum_k c_k x_k + zero * sum_k x_k)  -- which needs only x,
-//    scales and qzeros -- is computed per column while the first weight loads are in flight.
+//  * Weight stream: a producer warp copies the CTA's share of qweight into a shared-memory ring
+//    with bulk asynchronous copies (cp.async.bulk, one per 1 KB row segment, completion counted
+//    on an mbarrier).  It starts at the first instruction of the kernel, before the dependency on
+//    the previous kernel is awaited (weights are constants), so under programmatic dependent
+//    launch the next layer's weights are already landing while this layer finishes.
+//  * Unpack without shifts into place or integer->float conversion: a LOP3 masks two fields of a
+//    word and ORs in an fp16 exponent, which yields the half2 (c_lo + q_lo, c_hi + q_hi) with small
+//    known offsets c (8..128).
+//  * The products are done by mma.sync m16n8k16 (f16 x f16 -> f32): the 16 rows of the A tile
+//    are 16 output columns, the 8 columns of B are the (up to 8) rows of x, so one instruction
+//    retires 256 weights of a warp for every M <= 8.  Offsets and zero-points are removed
+//    afterwards: per group, sum_k (c_k + q_k) x_k is scaled by s, and
+//    sum_g s * (sum_k c_k x_k + zero * sum_k x_k) -- which needs only x, scales and qzeros -- is
+//    computed once per column while the weights are in flight.
 //
-// Work split: a "unit" is 256 columns x 32 rows (4-bit) or x 128 rows (3-bit).  Units are
-// numbered column-group-major and dealt out in equal contiguous ranges to 2 CTAs per SM,
-// so every shape is balanced; a range that ends inside a column group leaves a partial
-// sum in the fp32 scratch and the last CTA of that column group adds the partials in a
-// fixed order (results do not depend on scheduling).
+// Work split: a "unit" is 256 columns x 32 rows (4-bit) or x 128 rows (3-bit).  A thread-block
+// cluster of up to 8 CTAs owns one 256-column group and splits its K range evenly; the CTAs'
+// partial sums are combined through distributed shared memory by the cluster's first CTA in rank
+// order (results do not depend on scheduling; no global scratch, atomics or fences are involved).
+// The cluster size is the largest that still lets every CTA of the grid be resident at once.
+// Every mbarrier wait is bounded; if one expires the kernel raises a sticky status word and runs
+// on without waiting.
 //
 // Reference semantics: auto_gptq/nn_modules/qlinear.py:197-243; the kernel this replaces is
 // the TVM-generated SIMT GEMV src/kernels/gemv_kernel.cu:25-55.
 #include <cstdlib>
-#include <type_traits>
 
 #include "common.cuh"
 
@@ -35,18 +39,20 @@ namespace b200gptq {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarpsPerCta = kThreads / 32;
-constexpr int kCgCols = 32 * kWarpsPerCta;  // 256 columns per column group
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = 32 * kConsumerWarps;   // 256
+constexpr int kThreads = kConsumerThreads + 32;          // + the producer warp
+constexpr int kCgCols = 32 * kConsumerWarps;             // 256 columns per column group
 constexpr int kMaxM = 8;
-constexpr int kStageRows = 1024;            // rows of x staged in shared memory at a time
+constexpr int kMaxStageRows = 2048;         // rows of x staged in shared memory at a time (fewer when M is large)
+constexpr int kStageGroups = 16;            // and at most this many groups
+constexpr int kInflightBytes = 40 * 1024;   // weight bytes a CTA keeps in flight when two CTAs share an SM (measured:
+                                            // deeper rings push a CTA past half an SM and cost more than they gain)
+constexpr int kRowPitch = kCgCols * 4 + 32; // bytes between word-rows in the ring: conflict-free 128-bit reads
+constexpr int kMaxRing = 32;
+constexpr int kStatusWord = kMaxCounters - 1;
 
-__device__ __forceinline__ uint4 ldg_stream(const int32_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t magic) {
     uint32_t r;
@@ -62,6 +68,42 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  After ~1e9 clocks, or once any thread of the CTA has given up, waiting stops for
+// good: the kernel then finishes with undefined results and a raised status word instead of hanging.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+    while (!*gave_up) {
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return;
+        if (clock64() - t0 > 1000000000LL) *gave_up = 1;
+    }
+}
+// Bulk asynchronous copy global -> shared memory of this CTA; both addresses and the size are multiples of 16.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+
 // 3-bit: half index, inside a fragment entry, of the x value that meets field f of a row block.
 __constant__ unsigned char kSlot3[32] = {0, 2, 4, 6, 8, 1, 3, 5, 7, 9, 11, 12, 14, 16, 18, 20,
                                          13, 15, 17, 19, 21, 23, 24, 26, 28, 30, 32, 25, 27, 29, 31, 33};
@@ -69,7 +111,8 @@ __constant__ unsigned char kSlot3[32] = {0, 2, 4, 6, 8, 1, 3, 5, 7, 9, 11, 12, 1
 // ---------------------------------------------------------------------------------------
 // Per-bit-width traits.
 //   kUnitRows     rows of K covered by one unit
-//   kVecs         128-bit loads per thread per unit
+//   kWordRows     word-rows of qweight per unit (= rows of the unit's ring buffer)
+//   kVecs         128-bit reads per thread per unit
 //   kBRegs        32-bit registers of B fragments per (unit, x row, quad lane), padded to x4
 // Lane (g = lane/4, j = lane%4) of warp w holds columns 32w + 4g .. +3 of the column group.
 // ---------------------------------------------------------------------------------------
@@ -81,22 +124,14 @@ template <> struct Traits<4> {
     static constexpr int kUnitRows = 32;
     static constexpr int kVecs = 1;
     static constexpr int kBRegs = 4;
-    static constexpr int kDepth = 8;   // units in flight per thread
 
     static constexpr int kWordRows = 4;  // word-rows of qweight per unit
+    __device__ static __forceinline__ int lane_row(int j) { return j; }   // word-row of the unit read by quad lane j
 
-    // p points at word-row 4*kb + j of the lane's first column.
-    __device__ static __forceinline__ void load(uint4 (&buf)[kVecs], const int32_t* __restrict__ p, int N,
-                                                bool active) {
-        (void)N;
-        if (active) buf[0] = ldg_stream(p);
-        else buf[0] = make_uint4(0, 0, 0, 0);
-    }
-    __device__ static __forceinline__ int first_word_row(int kb, int j) { return 4 * kb + j; }
-
-    // d[cp] accumulates column pair cp (columns 2cp, 2cp+1 of the lane's 4) over this unit.
+    // d[cp] + d[2 + cp] accumulate column pair cp (columns 2cp, 2cp+1 of the lane's 4) over this unit;
+    // two accumulator sets halve the length of the dependent mma chains.
     __device__ static void compute(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm, bool has_x,
-                                   float (&d)[2][4]) {
+                                   float (&d)[4][4]) {
         uint4 bf = make_uint4(0, 0, 0, 0);
         if (has_x) bf = *reinterpret_cast<const uint4*>(bsm);
         const uint32_t wcol[4] = {buf[0].x, buf[0].y, buf[0].z, buf[0].w};
@@ -109,7 +144,7 @@ template <> struct Traits<4> {
             const uint32_t a_p2 = lop3_and_or(wa >> 4, MASK, MAGIC), b_p2 = lop3_and_or(wb >> 4, MASK, MAGIC);
             const uint32_t a_p3 = lop3_and_or(wa >> 8, MASK, MAGIC), b_p3 = lop3_and_or(wb >> 8, MASK, MAGIC);
             mma16816(d[cp], a_p0, b_p0, a_p1, b_p1, bf.x, bf.y);
-            mma16816(d[cp], a_p2, b_p2, a_p3, b_p3, bf.z, bf.w);
+            mma16816(d[2 + cp], a_p2, b_p2, a_p3, b_p3, bf.z, bf.w);  // second accumulator set: shorter chains
         }
     }
 
@@ -129,20 +164,9 @@ template <> struct Traits<3> {
     static constexpr int kUnitRows = 128;
     static constexpr int kVecs = 3;
     static constexpr int kBRegs = 20;  // 18 used
-    static constexpr int kDepth = 3;
 
     static constexpr int kWordRows = 12;
-
-    // p points at word-row 3*(4*kb + j) of the lane's first column.
-    __device__ static __forceinline__ void load(uint4 (&buf)[kVecs], const int32_t* __restrict__ p, int N,
-                                                bool active) {
-#pragma unroll
-        for (int r = 0; r < 3; ++r) {
-            if (active) buf[r] = ldg_stream(p + (size_t)r * N);
-            else buf[r] = make_uint4(0, 0, 0, 0);
-        }
-    }
-    __device__ static __forceinline__ int first_word_row(int kb, int j) { return 3 * (4 * kb + j); }
+    __device__ static __forceinline__ int lane_row(int j) { return 3 * j; }  // first of the 3 word-rows of quad lane j
 
     // Window t (0..8) of one column's stream (w0, w1, w2); stream offsets -4, 2, 8, 29, 35, 41, 62, 68, 74.
     template <int T_>
@@ -160,7 +184,7 @@ template <> struct Traits<3> {
 
     template <int T_>
     __device__ static __forceinline__ void step(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm,
-                                                bool has_x, float (&d)[2][4]) {
+                                                bool has_x, float (&d)[4][4]) {
         constexpr uint32_t MASK_A = 0x00380070u, MAGIC_A = 0x58005400u;  // (64 + f[b+1], 128 + f[b+6])
         constexpr uint32_t MASK_B = 0x01C00380u, MAGIC_B = 0x4C004800u;  // ( 8 + f[b+2],  16 + f[b+7])
         uint2 bf = make_uint2(0, 0);
@@ -168,19 +192,19 @@ template <> struct Traits<3> {
         {
             const uint32_t va = window<T_>(buf[0].x, buf[1].x, buf[2].x);
             const uint32_t vb = window<T_>(buf[0].y, buf[1].y, buf[2].y);
-            mma16816(d[0], lop3_and_or(va, MASK_A, MAGIC_A), lop3_and_or(vb, MASK_A, MAGIC_A),
+            mma16816(d[2 * (T_ & 1)], lop3_and_or(va, MASK_A, MAGIC_A), lop3_and_or(vb, MASK_A, MAGIC_A),
                      lop3_and_or(va, MASK_B, MAGIC_B), lop3_and_or(vb, MASK_B, MAGIC_B), bf.x, bf.y);
         }
         {
             const uint32_t va = window<T_>(buf[0].z, buf[1].z, buf[2].z);
             const uint32_t vb = window<T_>(buf[0].w, buf[1].w, buf[2].w);
-            mma16816(d[1], lop3_and_or(va, MASK_A, MAGIC_A), lop3_and_or(vb, MASK_A, MAGIC_A),
+            mma16816(d[2 * (T_ & 1) + 1], lop3_and_or(va, MASK_A, MAGIC_A), lop3_and_or(vb, MASK_A, MAGIC_A),
                      lop3_and_or(va, MASK_B, MAGIC_B), lop3_and_or(vb, MASK_B, MAGIC_B), bf.x, bf.y);
         }
     }
 
     __device__ static void compute(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm, bool has_x,
-                                   float (&d)[2][4]) {
+                                   float (&d)[4][4]) {
         step<0>(buf, bsm, has_x, d); step<1>(buf, bsm, has_x, d); step<2>(buf, bsm, has_x, d);
         step<3>(buf, bsm, has_x, d); step<4>(buf, bsm, has_x, d); step<5>(buf, bsm, has_x, d);
         step<6>(buf, bsm, has_x, d); step<7>(buf, bsm, has_x, d); step<8>(buf, bsm, has_x, d);
@@ -197,22 +221,37 @@ template <> struct Traits<3> {
 };
 
 struct Plan {
-    int cgs;          // column groups (256 columns each)
+    int cgs;          // column groups (256 columns each) = clusters
     int kbs;          // units per column group
-    int units;        // cgs * kbs
-    int ctas;
-    int stage_units;  // units whose x values are staged in shared memory at a time (<= 1024 rows, <= 8 groups)
+    int cluster;      // CTAs per cluster: the column group's K range is split evenly among them
+    int stage_units;  // units whose x values are staged in shared memory at a time
+    int ring_units;   // unit buffers in the shared-memory ring
 };
 
-__host__ __device__ inline int cta_first_unit(int i, int units, int ctas) {
-    return (int)(((long long)i * units) / ctas);
-}
-// CTA that owns unit u (largest i with cta_first_unit(i) <= u).
-__host__ __device__ inline int unit_owner(int u, int units, int ctas) {
-    return (int)((((long long)u + 1) * ctas - 1) / units);
-}
+// Rows of x staged at a time: the whole K slice of a CTA for the usual decode shapes.
+__host__ __device__ inline int max_stage_rows(int M) { return M <= 2 ? kMaxStageRows : (M <= 4 ? 1024 : 512); }
 
-constexpr int kStageGroups = 8;
+// Dynamic shared memory, in this order: ring | xs | s_sm | z_sm | corr_sm | ps
+template <int BITS> __host__ __device__ constexpr int unit_bytes() { return Traits<BITS>::kWordRows * kRowPitch; }
+template <int BITS> __host__ __device__ inline int xs_bytes(int M) {
+    return (max_stage_rows(M) / Traits<BITS>::kUnitRows) * M * 4 * Traits<BITS>::kBRegs * 4;
+}
+__host__ __device__ inline int s_sm_bytes() { return kStageGroups * kCgCols * 4; }
+__host__ __device__ inline int z_sm_bytes() { return kStageGroups * kCgCols * 4; }
+__host__ __device__ inline int corr_bytes(int M) { return M * kCgCols * 4; }
+__host__ __device__ inline int ps_bytes(int M) { return M * (max_stage_rows(M) / 8) * 8; }
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Read a float from the same shared-memory offset in CTA `rank` of this cluster.
+__device__ __forceinline__ float ld_cluster_f32(const float* local_ptr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_ptr)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
 
 #ifdef B200GPTQ_TRACE
 __device__ unsigned long long g_trace[1024 * 8];
@@ -220,209 +259,304 @@ __device__ __forceinline__ void trace_mark(int slot) {
     if (threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_trace[blockIdx.x * 8 + slot] = t;
+        if (g_trace[blockIdx.x * 8 + slot] == 0) g_trace[blockIdx.x * 8 + slot] = t;
     }
 }
+__global__ void trace_clear_kernel() { g_trace[blockIdx.x * blockDim.x + threadIdx.x] = 0; }
 #define TRACE(slot) trace_mark(slot)
 #else
 #define TRACE(slot)
 #endif
 
+// One cluster per column group; CTA `rank` of the cluster owns units [rank*kbs/C, (rank+1)*kbs/C).
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qweight,
                    const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
                    const int32_t* __restrict__ x_perm, const __half* __restrict__ bias, __half* __restrict__ y,
-                   int M, int K, int N, int group_size, Plan plan, float* __restrict__ partials,
-                   unsigned int* __restrict__ counters) {
+                   int M, int K, int N, int group_size, Plan plan, unsigned int* __restrict__ status) {
     using T = Traits<BITS>;
     constexpr int UR = T::kUnitRows;
-    constexpr int D = T::kDepth;
-    constexpr int MAX_STAGE_UNITS = kStageRows / UR;
+    constexpr int UB = unit_bytes<BITS>();
 
-    __shared__ __align__(16) uint32_t xs[MAX_STAGE_UNITS * kMaxM * 4 * T::kBRegs];  // x in fragment order
-    __shared__ float2 ps[kMaxM][kStageRows / 8];            // (sum x, sum c*x) of each 8 staged rows
-    __shared__ __align__(16) float s_sm[kStageGroups][kCgCols];  // scales of the staged groups
-    __shared__ float corr_sm[kMaxM][kCgCols];               // offset / zero-point term, then the segment result
+    extern __shared__ __align__(128) uint8_t dsm[];
+    __shared__ __align__(8) uint64_t bars[2 * kMaxRing];   // full[R], empty[R]
     __shared__ float t_x[kStageGroups * kMaxM], t_cx[kStageGroups * kMaxM];
-    __shared__ bool is_last;
+    __shared__ volatile int gave_up;
 
+    // Let the next kernel of the stream start its own weight stream as early as possible.
+    asm volatile("griddepcontrol.launch_dependents;");
     TRACE(0);
+
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, j = lane & 3;
-    const int u_begin = cta_first_unit(blockIdx.x, plan.units, plan.ctas);
-    const int u_end = cta_first_unit(blockIdx.x + 1, plan.units, plan.ctas);
-    const int kbs = plan.kbs;
-    const int zwords = N / 32 * BITS;
-    const int lane_col = warp * 32 + 4 * g;  // first of the lane's 4 columns inside the column group
-    const size_t unit_stride = (size_t)T::kWordRows * N;
-    const int units_per_group = group_size / UR;
+    const int R = plan.ring_units, C = plan.cluster, kbs = plan.kbs;
+    const int cg = blockIdx.x / C, rank = blockIdx.x - cg * C;
+    const int kb_begin = (int)(((long long)rank * kbs) / C), kb_end = (int)(((long long)(rank + 1) * kbs) / C);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxRing + s); };
 
-    // ---- the weight stream: a register ring of D units, refilled as it is consumed ----
-    int pf_cg = u_begin / kbs;
-    int pf_left_cg = kbs - (u_begin - pf_cg * kbs);   // units left in the prefetch column group
-    int pf_left = u_end - u_begin;                    // units left in this CTA's range
-    bool pf_col_ok = pf_cg * kCgCols + lane_col < N;
-    const int32_t* pf_ptr =
-        qweight + (size_t)T::first_word_row(kbs - pf_left_cg, j) * N + (size_t)pf_cg * kCgCols + lane_col;
-    auto prefetch = [&](uint4 (&dst)[T::kVecs]) {
-        T::load(dst, pf_ptr, N, pf_left > 0 && pf_col_ok);
-        pf_ptr += unit_stride;
-        --pf_left;
-        if (--pf_left_cg == 0) {
-            ++pf_cg;
-            pf_left_cg = kbs;
-            pf_col_ok = pf_cg * kCgCols + lane_col < N;
-            pf_ptr = qweight + (size_t)T::first_word_row(0, j) * N + (size_t)pf_cg * kCgCols + lane_col;
+    uint8_t* after_xs = dsm + (size_t)R * UB + xs_bytes<BITS>(M);
+    float (*s_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs);
+    float (*z_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs + s_sm_bytes());
+    float (*corr_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs + s_sm_bytes() + z_sm_bytes());
+    float2* ps = reinterpret_cast<float2*>(after_xs + s_sm_bytes() + z_sm_bytes() + corr_bytes(M));
+
+    if (tid == 0) {
+        gave_up = 0;
+        for (int s = 0; s < R; ++s) {
+            mbar_init(full_bar(s), 1);                 // the producer's expect_tx arrive
+            mbar_init(empty_bar(s), kConsumerWarps);   // one arrive per consumer warp
         }
-    };
-    uint4 buf[D][T::kVecs];
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
 
-#pragma unroll
-    for (int m = 0; m < kMaxM; ++m) corr_sm[m][tid] = 0.f;
+    if (warp == kConsumerWarps) {
+        // ===== producer warp: stream this CTA's units into the ring =====
+        int slot = 0, round = 0;
+        const int cols = min(kCgCols, N - cg * kCgCols);
+        const uint32_t row_bytes = (uint32_t)cols * 4u;
+        // start once the consumers have queued their first small loads (scales, zero-points)
+        asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (round > 0) mbar_wait(empty_bar(slot), (round - 1) & 1, &gave_up);
+            if (lane == 0) mbar_arrive_expect_tx(full_bar(slot), row_bytes * T::kWordRows);
+            __syncwarp();
+            if (lane < T::kWordRows) {
+                const int32_t* src = qweight + (size_t)(kb * T::kWordRows + lane) * N + (size_t)cg * kCgCols;
+                bulk_copy_g2s(smem_u32(dsm) + slot * UB + lane * kRowPitch, src, row_bytes, full_bar(slot));
+            }
+            if (++slot == R) { slot = 0; ++round; }
+        }
+    } else {
+        // ===== consumer warps =====
+        const int g = lane >> 2, j = lane & 3;
+        const int zwords = N / 32 * BITS;
+        const int lane_col = warp * 32 + 4 * g;  // first of the lane's 4 columns inside the column group
+        const int units_per_group = group_size / UR;
+        uint32_t* xs = reinterpret_cast<uint32_t*>(dsm + (size_t)R * UB);
+        const int ps_pitch = max_stage_rows(M) / 8;   // ps[m * ps_pitch + octet]: (sum x, sum c*x) of 8 staged rows
+        const uint32_t lane_off = (uint32_t)(T::lane_row(j) * kRowPitch + lane_col * 4);
 
-    float out[2][4], d[2][4];
-#pragma unroll
-    for (int cp = 0; cp < 2; ++cp)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) { out[cp][r] = 0.f; d[cp][r] = 0.f; }
+        for (int m = 0; m < M; ++m) corr_sm[m][tid] = 0.f;
 
-    bool waited = false;
-    int stage_g0 = 0;
-
-    // out += scale[group] * d for the lane's 4 columns, then clear d.
-    auto flush_group = [&](int grp) {
-        const float4 s = *reinterpret_cast<const float4*>(&s_sm[grp - stage_g0][lane_col]);
-        out[0][0] = fmaf(s.x, d[0][0], out[0][0]); out[0][1] = fmaf(s.x, d[0][1], out[0][1]);
-        out[0][2] = fmaf(s.y, d[0][2], out[0][2]); out[0][3] = fmaf(s.y, d[0][3], out[0][3]);
-        out[1][0] = fmaf(s.z, d[1][0], out[1][0]); out[1][1] = fmaf(s.z, d[1][1], out[1][1]);
-        out[1][2] = fmaf(s.w, d[1][2], out[1][2]); out[1][3] = fmaf(s.w, d[1][3], out[1][3]);
+        float out[2][4], d[4][4];
 #pragma unroll
         for (int cp = 0; cp < 2; ++cp)
 #pragma unroll
-            for (int r = 0; r < 4; ++r) d[cp][r] = 0.f;
-    };
+            for (int r = 0; r < 4; ++r) { out[cp][r] = 0.f; d[cp][r] = 0.f; d[2 + cp][r] = 0.f; }
 
-    // Stage x for units [kb_a, kb_b) of column group cg: fragments into xs, scales into s_sm, and
-    // the offset / zero-point term  sum_groups s * (sum c x + zero * sum x)  into corr_sm.
-    auto stage = [&](int cg, int kb_a, int kb_b) {
-        const int r0 = kb_a * UR, rows = (kb_b - kb_a) * UR;
-        const int g0 = r0 / group_size, ng = (r0 + rows - 1) / group_size - g0 + 1;
-        const int n = min(cg * kCgCols + tid, N - 1);
-        // -- static data first: scales and zero-points of this thread's column, gather indices
-        int zw, zsh;
-        bool zstr = false;
-        if constexpr (BITS == 3) {
-            const int bit = 3 * (n & 31);
-            zw = 3 * (n >> 5) + (bit >> 5); zsh = bit & 31; zstr = zsh > 29;
-        } else {
-            zw = n >> 3; zsh = 4 * (n & 7);
-        }
-        const __half* sp = scales + (size_t)g0 * N + n;
-        const uint32_t* zp = reinterpret_cast<const uint32_t*>(qzeros) + (size_t)g0 * zwords + zw;
-        float s_reg[kStageGroups], z_reg[kStageGroups];
+        bool first_stage = true;
+        int stage_g0 = 0;
+
+        // out += scale[group] * d for the lane's 4 columns, then clear d.
+        auto flush_group = [&](int grp) {
+            const float4 s = *reinterpret_cast<const float4*>(&s_sm[grp - stage_g0][lane_col]);
+            out[0][0] = fmaf(s.x, d[0][0] + d[2][0], out[0][0]); out[0][1] = fmaf(s.x, d[0][1] + d[2][1], out[0][1]);
+            out[0][2] = fmaf(s.y, d[0][2] + d[2][2], out[0][2]); out[0][3] = fmaf(s.y, d[0][3] + d[2][3], out[0][3]);
+            out[1][0] = fmaf(s.z, d[1][0] + d[3][0], out[1][0]); out[1][1] = fmaf(s.z, d[1][1] + d[3][1], out[1][1]);
+            out[1][2] = fmaf(s.w, d[1][2] + d[3][2], out[1][2]); out[1][3] = fmaf(s.w, d[1][3] + d[3][3], out[1][3]);
 #pragma unroll
-        for (int gl = 0; gl < kStageGroups; ++gl) {
-            s_reg[gl] = 0.f; z_reg[gl] = 0.f;
-            if (gl < ng) {
-                s_reg[gl] = __half2float(__ldg(sp + (size_t)gl * N));
-                const uint32_t lo = __ldg(zp + (size_t)gl * zwords);
-                uint32_t q;
-                if constexpr (BITS == 3) {
-                    const uint32_t hi = zstr ? __ldg(zp + (size_t)gl * zwords + 1) : 0u;
-                    q = __funnelshift_r(lo, hi, zsh) & 7u;
-                } else {
-                    q = (lo >> zsh) & 15u;
-                }
-                z_reg[gl] = __uint_as_float(0x4B000000u | (q + 1u)) - 8388608.f;  // exact small integer
+            for (int cp = 0; cp < 4; ++cp)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) d[cp][r] = 0.f;
+        };
+
+        // Stage x for units [kb_a, kb_b): fragments into xs, scales and zero-points into s_sm / z_sm, and
+        // the offset / zero-point term  sum_groups s * (sum c x + zero * sum x)  into corr_sm.
+        auto stage = [&](int kb_a, int kb_b) {
+            const int r0 = kb_a * UR, rows = (kb_b - kb_a) * UR;
+            const int g0 = r0 / group_size, ng = (r0 + rows - 1) / group_size - g0 + 1;
+            const int n = min(cg * kCgCols + tid, N - 1);
+            int zw, zsh;
+            bool zstr = false;
+            if constexpr (BITS == 3) {
+                const int bit = 3 * (n & 31);
+                zw = 3 * (n >> 5) + (bit >> 5); zsh = bit & 31; zstr = zsh > 29;
+            } else {
+                zw = n >> 3; zsh = 4 * (n & 7);
             }
-        }
-        const bool has_q = tid < rows / 4;
-        const int kq = r0 + 4 * tid;  // this thread stages rows kq .. kq+3 of every x row
-        int4 pidx = make_int4(kq, kq + 1, kq + 2, kq + 3);
-        if (has_q && x_perm) pidx = __ldg(reinterpret_cast<const int4*>(x_perm + kq));
-        if (!waited) {
-            // The small loads above are already queued; now start the weight stream behind them.
-#pragma unroll
-            for (int i = 0; i < D; ++i) prefetch(buf[i]);
-            // x is the only operand a preceding kernel may still be writing
-            asm volatile("griddepcontrol.launch_dependents;");
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            waited = true;
-            TRACE(1);
-        }
-        __syncthreads();  // the previous stage's fragments and scales are no longer in use
-#pragma unroll
-        for (int gl = 0; gl < kStageGroups; ++gl) s_sm[gl][tid] = s_reg[gl];
-        {
-            const int kl = 4 * tid;                               // row inside the stage
-            const int ul = kl / UR, jl = (kl % UR) / T::kRowsPerLane, f0 = kl % T::kRowsPerLane;
+            const __half* sp = scales + (size_t)g0 * N + n;
+            const uint32_t* zp = reinterpret_cast<const uint32_t*>(qzeros) + (size_t)g0 * zwords + zw;
             __half* xh = reinterpret_cast<__half*>(xs);
+            consumer_sync();  // the previous stage's fragments, scales and zero-points are no longer in use
+
+            // 4 rows of K of up to 4 rows of x per thread and pass
+            auto x_issue = [&](int qi, int m0, int4 pidx, __half (&v)[4][4]) {
+                const int kq = r0 + 4 * qi;
+#pragma unroll
+                for (int mm = 0; mm < 4; ++mm) {
+                    const int m = m0 + mm;
+                    if (qi < rows / 4 && m < M) {
+                        const __half* xr = x + (size_t)m * K;
+                        if (x_perm) {
+                            v[mm][0] = xr[pidx.x]; v[mm][1] = xr[pidx.y]; v[mm][2] = xr[pidx.z]; v[mm][3] = xr[pidx.w];
+                        } else {
+                            const uint2 raw = *reinterpret_cast<const uint2*>(xr + kq);
+                            v[mm][0] = __ushort_as_half((unsigned short)(raw.x & 0xffffu));
+                            v[mm][1] = __ushort_as_half((unsigned short)(raw.x >> 16));
+                            v[mm][2] = __ushort_as_half((unsigned short)(raw.y & 0xffffu));
+                            v[mm][3] = __ushort_as_half((unsigned short)(raw.y >> 16));
+                        }
+                    }
+                }
+            };
+            auto x_consume = [&](int qi, int m0, const __half (&v)[4][4]) {
+                const bool has_q = qi < rows / 4;
+                const int kl = 4 * qi;                                // row inside the stage
+                const int ul = kl / UR, jl = (kl % UR) / T::kRowsPerLane, f0 = kl % T::kRowsPerLane;
+#pragma unroll
+                for (int mm = 0; mm < 4; ++mm) {
+                    const int m = m0 + mm;
+                    if (m < M) {  // uniform
+                        float sx = 0.f, scx = 0.f;
+                        if (has_q) {
+                            __half* e = xh + (size_t)(((ul * M + m) * 4 + jl) * T::kBRegs) * 2;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int h = T::slot(f0 + i);
+                                e[h] = v[mm][i];
+                                const float xf = __half2float(v[mm][i]);
+                                sx += xf;
+                                scx = fmaf(T::coef(h), xf, scx);
+                            }
+                            if (BITS == 3 && f0 == 0) {  // slots that no field feeds must multiply by zero
+                                const __half zero = __float2half(0.f);
+                                e[10] = zero; e[22] = zero; e[34] = zero; e[35] = zero;
+                            }
+                        }
+                        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+                        scx += __shfl_xor_sync(0xffffffffu, scx, 1);
+                        if (has_q && (tid & 1) == 0) ps[m * ps_pitch + (qi >> 1)] = make_float2(sx, scx);
+                    }
+                }
+            };
+            auto perm_of = [&](int qi) {
+                const int kq = r0 + 4 * qi;
+                int4 pidx = make_int4(kq, kq + 1, kq + 2, kq + 3);
+                if (qi < rows / 4 && x_perm) pidx = __ldg(reinterpret_cast<const int4*>(x_perm + kq));
+                return pidx;
+            };
+
+            // -- constants (scales, zero-points, gather indices): 8 groups of loads in flight at a time; the
+            //    first pass of x loads is issued before the first constants are consumed, so that a stage
+            //    costs one round trip to memory, not two
+            __half v0[4][4];
+            const int4 pidx0 = perm_of(tid);
+#pragma unroll 1
+            for (int gb = 0; gb < ng; gb += 8) {
+                __half sv[8];
+                uint32_t lo[8], hi[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    sv[i] = __float2half(0.f); lo[i] = 0u; hi[i] = 0u;
+                    if (gb + i < ng) {
+                        sv[i] = __ldg(sp + (size_t)(gb + i) * N);
+                        lo[i] = __ldg(zp + (size_t)(gb + i) * zwords);
+                        if (BITS == 3 && zstr) hi[i] = __ldg(zp + (size_t)(gb + i) * zwords + 1);
+                    }
+                }
+                if (gb == 0) {
+                    if (first_stage) {
+                        // these loads are queued; now the producer may flood the memory system with weight copies
+                        asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
+                        // x is the only operand a preceding kernel may still be writing
+                        asm volatile("griddepcontrol.wait;" ::: "memory");
+                        first_stage = false;
+                    }
+                    x_issue(tid, 0, pidx0, v0);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (gb + i < ng) {
+                        uint32_t q;
+                        if constexpr (BITS == 3) q = __funnelshift_r(lo[i], hi[i], zsh) & 7u;
+                        else q = (lo[i] >> zsh) & 15u;
+                        s_sm[gb + i][tid] = __half2float(sv[i]);
+                        z_sm[gb + i][tid] = __uint_as_float(0x4B000000u | (q + 1u)) - 8388608.f;  // exact small integer
+                    }
+                }
+            }
+            TRACE(1);
+            x_consume(tid, 0, v0);
+#pragma unroll 1
+            for (int q0 = 0; q0 < rows / 4; q0 += kConsumerThreads) {
+                const int qi = q0 + tid;
+                const int4 pidx = q0 == 0 ? pidx0 : perm_of(qi);
+#pragma unroll 1
+                for (int m0 = (q0 == 0 ? 4 : 0); m0 < M; m0 += 4) {
+                    __half v[4][4];
+                    x_issue(qi, m0, pidx, v);
+                    x_consume(qi, m0, v);
+                }
+            }
+            consumer_sync();
+            TRACE(3);
+            if (tid < ng * M) {
+                const int m = tid % M, gl = tid / M;
+                const int ra = max(r0, (g0 + gl) * group_size), rb = min(r0 + rows, (g0 + gl + 1) * group_size);
+                float sx = 0.f, scx = 0.f;
+#pragma unroll 4
+                for (int o = (ra - r0) >> 3; o < (rb - r0) >> 3; ++o) {
+                    const float2 p = ps[m * ps_pitch + o];
+                    sx += p.x;
+                    scx += p.y;
+                }
+                t_x[gl * kMaxM + m] = sx;
+                t_cx[gl * kMaxM + m] = scx;
+            }
+            consumer_sync();
 #pragma unroll 1
             for (int m = 0; m < M; ++m) {
-                float sx = 0.f, scx = 0.f;
-                if (has_q) {
-                    const __half* xr = x + (size_t)m * K;
-                    __half v[4];
-                    if (x_perm) {
-                        v[0] = xr[pidx.x]; v[1] = xr[pidx.y]; v[2] = xr[pidx.z]; v[3] = xr[pidx.w];
-                    } else {
-                        const uint2 raw = *reinterpret_cast<const uint2*>(xr + kq);
-                        v[0] = __ushort_as_half((unsigned short)(raw.x & 0xffffu));
-                        v[1] = __ushort_as_half((unsigned short)(raw.x >> 16));
-                        v[2] = __ushort_as_half((unsigned short)(raw.y & 0xffffu));
-                        v[3] = __ushort_as_half((unsigned short)(raw.y >> 16));
-                    }
-                    __half* e = xh + (size_t)(((ul * M + m) * 4 + jl) * T::kBRegs) * 2;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int h = T::slot(f0 + i);
-                        e[h] = v[i];
-                        const float xf = __half2float(v[i]);
-                        sx += xf;
-                        scx = fmaf(T::coef(h), xf, scx);
-                    }
-                    if (BITS == 3 && f0 == 0) {  // slots that no field feeds must multiply by zero
-                        const __half zero = __float2half(0.f);
-                        e[10] = zero; e[22] = zero; e[34] = zero; e[35] = zero;
-                    }
-                }
-                sx += __shfl_xor_sync(0xffffffffu, sx, 1);
-                scx += __shfl_xor_sync(0xffffffffu, scx, 1);
-                if (has_q && (tid & 1) == 0) ps[m][tid >> 1] = make_float2(sx, scx);
-            }
-        }
-        __syncthreads();
-        if (tid < ng * M) {
-            const int m = tid % M, gl = tid / M;
-            const int ra = max(r0, (g0 + gl) * group_size), rb = min(r0 + rows, (g0 + gl + 1) * group_size);
-            float sx = 0.f, scx = 0.f;
+                float c = 0.f;
 #pragma unroll 4
-            for (int o = (ra - r0) >> 3; o < (rb - r0) >> 3; ++o) {
-                const float2 p = ps[m][o];
-                sx += p.x;
-                scx += p.y;
+                for (int gl = 0; gl < ng; ++gl)
+                    c = fmaf(s_sm[gl][tid], fmaf(z_sm[gl][tid], t_x[gl * kMaxM + m], t_cx[gl * kMaxM + m]), c);
+                corr_sm[m][tid] += c;
             }
-            t_x[gl * kMaxM + m] = sx;
-            t_cx[gl * kMaxM + m] = scx;
-        }
-        __syncthreads();
-#pragma unroll 1
-        for (int m = 0; m < M; ++m) {
-            float c = 0.f;
-#pragma unroll
-            for (int gl = 0; gl < kStageGroups; ++gl)
-                if (gl < ng) c = fmaf(s_reg[gl], fmaf(z_reg[gl], t_x[gl * kMaxM + m], t_cx[gl * kMaxM + m]), c);
-            corr_sm[m][tid] += c;
-        }
-        stage_g0 = g0;
-        TRACE(2);
-    };
+            stage_g0 = g0;
+            TRACE(4);
+        };
 
-    // Close the segment of column group cg: combine lanes, remove the offset / zero-point term,
-    // then write y or leave the partial sums in the scratch for the last CTA of the column group.
-    auto finish_segment = [&](int cg) {
-        __syncthreads();  // corr_sm is complete
+        int kb = kb_begin, slot = 0, round = 0;
+        int grp = 0;
+        bool pending = false;  // d holds products that have not been scaled into out yet
+        while (kb < kb_end) {
+            // stage as far as the stage grid and this CTA's range allow
+            const int su = plan.stage_units;
+            const int kb_stop = min((kb / su + 1) * su, kb_end);
+            stage(kb, kb_stop);
+            grp = (kb * UR) / group_size;
+            int grp_left = units_per_group - (kb - grp * units_per_group);
+            const uint32_t* bsm = xs + (size_t)(g * 4 + j) * T::kBRegs;
+            const int bsm_step = M * 4 * T::kBRegs;
+#pragma unroll 1
+            for (; kb < kb_stop; ++kb) {
+                mbar_wait(full_bar(slot), round & 1, &gave_up);
+                uint4 cur[T::kVecs];
+                const uint8_t* src = dsm + slot * UB + lane_off;
+#pragma unroll
+                for (int r = 0; r < T::kVecs; ++r) cur[r] = *reinterpret_cast<const uint4*>(src + r * kRowPitch);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(slot));  // the unit is in registers: the producer may refill the slot
+                if (++slot == R) { slot = 0; ++round; }
+                T::compute(cur, bsm, g < M, d);
+                bsm += bsm_step;
+                pending = true;
+                if (--grp_left == 0) {
+                    flush_group(grp);
+                    ++grp;
+                    grp_left = units_per_group;
+                    pending = false;
+                }
+            }
+            TRACE(5);
+        }
+        if (pending) flush_group(grp);
+
+        // ---- this CTA's partial result: combine the lanes, remove the offset / zero-point term ----
+        consumer_sync();  // corr_sm is complete
 #pragma unroll
         for (int cp = 0; cp < 2; ++cp)
 #pragma unroll
@@ -430,112 +564,28 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
                 const int m = 2 * j + (r & 1);
                 const int c = lane_col + 2 * cp + (r >> 1);
                 if (m < M) corr_sm[m][c] = out[cp][r] - corr_sm[m][c];
-                out[cp][r] = 0.f;
             }
-        __syncthreads();
+        consumer_sync();
+    }
+
+    // ---- combine the K slices of the cluster through distributed shared memory, in rank order ----
+    if (C > 1) cluster_sync_all();   // every CTA's partial result is in its corr_sm
+    TRACE(6);
+    if (rank == 0 && warp < kConsumerWarps) {
         const int n = cg * kCgCols + tid;
-        const int owner_first = unit_owner(cg * kbs, plan.units, plan.ctas);
-        const int owner_last = unit_owner(cg * kbs + kbs - 1, plan.units, plan.ctas);
-        const bool whole = (owner_first == owner_last);
+        if (n < N) {
 #pragma unroll 1
-        for (int m = 0; m < M; ++m) {
-            float v = corr_sm[m][tid];
-            corr_sm[m][tid] = 0.f;
-            if (n < N) {
-                if (whole) {
-                    if (bias) v += __half2float(bias[n]);
-                    y[(size_t)m * N + n] = __float2half_rn(v);
-                } else {
-                    partials[((size_t)(blockIdx.x + cg) * kMaxM + m) * kCgCols + tid] = v;
-                }
+            for (int m = 0; m < M; ++m) {
+                float v = corr_sm[m][tid];
+                for (int r = 1; r < C; ++r) v += ld_cluster_f32(&corr_sm[m][tid], (uint32_t)r);
+                if (bias) v += __half2float(bias[n]);
+                y[(size_t)m * N + n] = __float2half_rn(v);
             }
-        }
-        if (!whole) {
-            __threadfence();
-            __syncthreads();
-            if (tid == 0) {
-                const unsigned int expected = (unsigned int)(owner_last - owner_first + 1);
-                const unsigned int prev = atomicAdd(counters + cg, 1u);
-                is_last = (prev == expected - 1);
-                if (is_last) counters[cg] = 0u;  // the scratch is left ready for the next call
-            }
-            __syncthreads();
-            if (is_last) {
-                __threadfence();
-                if (n < N) {
-#pragma unroll 1
-                    for (int m = 0; m < M; ++m) {
-                        float v = 0.f;
-#pragma unroll 4
-                        for (int i = owner_first; i <= owner_last; ++i)
-                            v += __ldcg(partials + ((size_t)(i + cg) * kMaxM + m) * kCgCols + tid);
-                        if (bias) v += __half2float(bias[n]);
-                        y[(size_t)m * N + n] = __float2half_rn(v);
-                    }
-                }
-            }
-        }
-    };
-
-    // One unit: take slot I of the register ring, refill it with the unit D ahead, multiply.
-    // The ring slot is a compile-time constant, so the switch below enters an unrolled sequence of D
-    // units at the current slot; the heavy, rarely executed stage / finish code exists once.
-    int u = u_begin, slot = 0;
-    int grp = 0, grp_left = 1;       // group of the next unit, units of it still to come
-    const uint32_t* bsm = xs;        // fragments of the next unit for this lane
-    const int bsm_step = M * 4 * T::kBRegs;
-    bool pending = false;            // d holds products that have not been scaled into out yet
-    auto unit = [&](auto slot_c) {
-        constexpr int I = decltype(slot_c)::value;
-        uint4 cur[T::kVecs];
-#pragma unroll
-        for (int r = 0; r < T::kVecs; ++r) cur[r] = buf[I][r];
-        prefetch(buf[I]);
-        T::compute(cur, bsm, g < M, d);
-        bsm += bsm_step;
-        ++u;
-        pending = true;
-        if (--grp_left == 0) {
-            flush_group(grp);
-            ++grp;
-            grp_left = units_per_group;
-            pending = false;
-        }
-    };
-
-    while (u < u_end) {
-        const int cg = u / kbs;
-        const int kb = u - cg * kbs;
-        // stage as far as the stage grid, the column group and this CTA's range allow
-        const int su = plan.stage_units;
-        const int kb_stop = min(min(kbs, (kb / su + 1) * su), kb + (u_end - u));
-        stage(cg, kb, kb_stop);
-        grp = (kb * UR) / group_size;
-        grp_left = units_per_group - (kb - grp * units_per_group);
-        bsm = xs + (size_t)(g * 4 + j) * T::kBRegs;
-        const int run_end = u + (kb_stop - kb);
-        while (u < run_end) {
-            switch (slot) {
-#define B200GPTQ_UNIT(I)                                             \
-    case I:                                                          \
-        if constexpr (I < D) {                                       \
-            unit(std::integral_constant<int, I>{});                  \
-            if (u == run_end) { slot = (I + 1) % D; break; }         \
-        }
-                B200GPTQ_UNIT(0) B200GPTQ_UNIT(1) B200GPTQ_UNIT(2) B200GPTQ_UNIT(3)
-                B200GPTQ_UNIT(4) B200GPTQ_UNIT(5) B200GPTQ_UNIT(6) B200GPTQ_UNIT(7)
-#undef B200GPTQ_UNIT
-                default: slot = 0;
-            }
-        }
-        TRACE(3);
-        // the segment ends here if the next unit belongs to another column group or to another CTA
-        if (u == u_end || kb_stop == kbs) {
-            if (pending) { flush_group(grp); pending = false; }
-            finish_segment(cg);
         }
     }
-    TRACE(4);
+    if (C > 1) cluster_sync_all();   // the other CTAs keep their shared memory alive until it has been read
+    if (tid == 0 && gave_up) atomicExch(status + kStatusWord, 1u);
+    TRACE(7);
 }
 
 int ctas_per_sm() {
@@ -547,20 +597,42 @@ int ctas_per_sm() {
     return v;
 }
 
-Plan make_plan(int K, int N, int bits, int group_size) {
+template <int BITS>
+Plan make_plan(int M, int K, int N, int group_size, int* smem_bytes) {
     Plan p;
-    const int unit_rows = bits == 4 ? Traits<4>::kUnitRows : Traits<3>::kUnitRows;
+    constexpr int unit_rows = Traits<BITS>::kUnitRows;
     p.cgs = (N + kCgCols - 1) / kCgCols;
     p.kbs = K / unit_rows;
-    p.units = p.cgs * p.kbs;
-    const int want = ctas_per_sm() * sm_count();
-    p.ctas = p.units < want ? p.units : want;
-    if (p.ctas < 1) p.ctas = 1;
-    // a stage spans at most kStageRows rows and at most kStageGroups groups, and starts on a multiple of itself
+    // cluster size: as many K slices as keep every CTA of the grid resident at once, at most 8.  With one
+    // CTA per SM a CTA can hold its whole slice in flight; with two, consecutive kernels can overlap.
+    const int per_sm = ctas_per_sm();
+    const int slots = per_sm * sm_count();
+    int c = slots / p.cgs;
+    if (c > 8) c = 8;
+    if (c > p.kbs) c = p.kbs;
+    if (c < 1) c = 1;
+    p.cluster = c;
+    // a stage spans at most max_stage_rows(M) rows and at most kStageGroups groups, and starts on a multiple of itself
+    const int cap = max_stage_rows(M);
     long long stage_rows = (long long)kStageGroups * group_size;
-    if (stage_rows > kStageRows) stage_rows = group_size <= kStageRows ? (kStageRows / group_size) * group_size : kStageRows;
+    if (stage_rows > cap) stage_rows = group_size <= cap ? (cap / group_size) * group_size : cap;
     p.stage_units = (int)(stage_rows / unit_rows);
     if (p.stage_units < 1) p.stage_units = 1;
+    // ring: enough unit buffers to cover the bandwidth-delay product, no more than the slice needs
+    const int other = xs_bytes<BITS>(M) + s_sm_bytes() + z_sm_bytes() + corr_bytes(M) + ps_bytes(M);
+    static const int inflight_env = [] {
+        const char* e = std::getenv("B200GPTQ_GEMV_INFLIGHT_KB");
+        const int kb = e ? std::atoi(e) : 0;
+        return kb > 0 ? kb * 1024 : 0;
+    }();
+    const int inflight = inflight_env ? inflight_env : (per_sm == 1 ? 3 * kInflightBytes : kInflightBytes);
+    int ring = (inflight + unit_bytes<BITS>() - 1) / unit_bytes<BITS>();
+    const int longest = (p.kbs + c - 1) / c;
+    if (ring > longest) ring = longest;
+    if (ring > kMaxRing) ring = kMaxRing;
+    if (ring < 2) ring = 2;
+    p.ring_units = ring;
+    *smem_bytes = ring * unit_bytes<BITS>() + other;
     return p;
 }
 
@@ -576,23 +648,39 @@ template <int BITS>
 int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                   const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int group_size,
                   void* workspace, cudaStream_t stream) {
-    const Plan plan = make_plan(K, N, BITS, group_size);
-    if (plan.cgs >= kMaxCounters - 1) return B200GPTQ_ERR_TOO_LARGE;  // the last counter word is reserved
-    unsigned int* counters = reinterpret_cast<unsigned int*>(workspace);
-    float* partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
+    int smem_bytes = 0;
+    const Plan plan = make_plan<BITS>(M, K, N, group_size, &smem_bytes);
+    unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
 
+    static bool attr_set[64] = {};
+    int dev = 0;
+    B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               200 * 1024));
+        attr_set[dev] = true;
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(plan.ctas);
+    cfg.gridDim = dim3(plan.cgs * plan.cluster);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = plan.cluster;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+    if (pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = na;
     B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS>, x, qweight, qzeros, scales, x_perm, bias, y,
-                                         M, K, N, group_size, plan, partials, counters));
+                                         M, K, N, group_size, plan, status));
     return B200GPTQ_OK;
 }
 
@@ -601,6 +689,10 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
 #ifdef B200GPTQ_TRACE
 extern "C" __attribute__((visibility("default"))) int b200gptq_trace_read(unsigned long long* host, int n) {
     return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n);
+}
+extern "C" __attribute__((visibility("default"))) int b200gptq_trace_clear(void) {
+    trace_clear_kernel<<<8, 1024>>>();
+    return (int)cudaDeviceSynchronize();
 }
 #endif
 
@@ -618,8 +710,8 @@ size_t gemv_stream_workspace_bytes(int M, int K, int N, int bits) {
     (void)M;
     if (bits != 3 && bits != 4) return 0;
     if (bits == 3 && K % 128 != 0) return 0;
-    const Plan plan = make_plan(K, N, bits, 128);
-    return kCounterBytes + (size_t)(plan.ctas + plan.cgs) * kMaxM * kCgCols * sizeof(float);
+    (void)K; (void)N;
+    return kCounterBytes;  // only the status word: partial sums travel through distributed shared memory
 }
 
 int gemv_stream_dispatch(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,

@@ -1,0 +1,267 @@
+"""Decoder harness around the QuantLinear path: Llama- and OPT-architecture models whose
+linears are synthetic GPTQ layers, with tensor parallelism over ``torch.distributed``.
+
+This is the step either side of the linears that the reference leaves to ``transformers``
+(its benchmark drives ``model.generate``: ``end2end/autogptq-generation-inference-benchmark.py:26-49``,
+``quantization/opt.py:306-354``).  Here it is a small explicit model so that one decode step can
+be captured in a CUDA graph and the linears can be sharded:
+
+* column-parallel (no exchange): fused q/k/v and fused gate/up (OPT: fc1) -- each rank owns a slice
+  of the output features, i.e. whole attention heads and a slice of the FFN width;
+* row-parallel (one all-reduce): o_proj and down_proj (OPT: out_proj, fc2) -- each rank owns the
+  matching slice of the input features, cut on quantisation-group boundaries;
+* the vocabulary projection stays dense fp16 (``modeling/_base.py:534`` keeps lm_head out of the
+  quantised set) and is sharded over the vocabulary; ranks exchange their best (logit, token).
+
+Weights are random (no checkpoints offline): every rank draws its own shards directly with the
+shapes and value distributions of the benchmark configuration, so the full model is never
+materialised on one device.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import synth
+from .qlinear import QuantLinear
+
+
+@dataclass
+class DecoderConfig:
+    arch: str = "llama"            # "llama" (RMSNorm, RoPE, SwiGLU) or "opt" (LayerNorm, learned positions, ReLU)
+    layers: int = 32
+    hidden: int = 4096
+    heads: int = 32
+    inter: int = 11008
+    vocab: int = 32000
+    bits: int = 4
+    group_size: int = 128
+    desc_act: bool = False
+    max_seq: int = 768
+    rope_theta: float = 10000.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.heads
+
+
+LLAMA_7B = DecoderConfig()
+OPT_66B = DecoderConfig(arch="opt", layers=64, hidden=9216, heads=72, inter=36864, vocab=50272, bits=3,
+                        group_size=128, desc_act=True, max_seq=256)
+
+
+def split_even(total: int, parts: int, unit: int) -> List[int]:
+    """Split ``total`` (a multiple of ``unit``) into ``parts`` multiples of ``unit``, as evenly as possible."""
+    n = total // unit
+    base, extra = divmod(n, parts)
+    return [(base + (1 if r < extra else 0)) * unit for r in range(parts)]
+
+
+def _make_qlinear(cfg: DecoderConfig, K: int, N: int, bias: bool, seed: int, device) -> QuantLinear:
+    layer = synth.make_layer(cfg.bits, K, N, cfg.group_size, cfg.desc_act, bias=bias, seed=seed, device=device)
+    m = QuantLinear(cfg.bits, cfg.group_size, K, N, bias)
+    m.qweight, m.qzeros, m.scales, m.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
+    if bias:
+        m.bias = layer.bias
+    m = m.to(device)
+    m.post_init()
+    if m._x_perm is not None:
+        m.qweight = m._qweight_run      # keep only the re-ordered copy of the weights
+        m.g_idx = m._g_idx_run if m._g_idx_run is not None else \
+            (torch.arange(K, device=device) // cfg.group_size).to(torch.int32)
+        m._ready_for = (m.qweight.device, m.qweight.data_ptr(), m.g_idx.data_ptr())
+    return m
+
+
+class DecoderLayer:
+    def __init__(self, cfg: DecoderConfig, idx: int, rank: int, world: int, device):
+        self.cfg = cfg
+        hd = cfg.head_dim
+        heads_local = split_even(cfg.heads, world, 1)[rank]
+        inter_local = split_even(cfg.inter, world, cfg.group_size)[rank]
+        self.heads_local, self.inter_local = heads_local, inter_local
+        attn_local = heads_local * hd
+        bias = cfg.arch == "opt"
+        seed = 100000 * rank + 10 * idx
+        self.qkv = _make_qlinear(cfg, cfg.hidden, 3 * attn_local, bias, seed + 1, device)
+        self.o = _make_qlinear(cfg, attn_local, cfg.hidden, bias and rank == 0, seed + 2, device)
+        n_up = (2 if cfg.arch == "llama" else 1) * inter_local
+        self.up = _make_qlinear(cfg, cfg.hidden, n_up, bias, seed + 3, device)
+        self.down = _make_qlinear(cfg, inter_local, cfg.hidden, bias and rank == 0, seed + 4, device)
+        g = torch.Generator(device=device).manual_seed(seed + 5)
+        self.norm1_w = 1.0 + 0.01 * torch.randn(cfg.hidden, generator=g, device=device, dtype=torch.float16)
+        self.norm2_w = 1.0 + 0.01 * torch.randn(cfg.hidden, generator=g, device=device, dtype=torch.float16)
+        self.norm1_b = self.norm2_b = None
+        if cfg.arch == "opt":
+            self.norm1_b = torch.zeros(cfg.hidden, device=device, dtype=torch.float16)
+            self.norm2_b = torch.zeros(cfg.hidden, device=device, dtype=torch.float16)
+        self.k_cache: Optional[torch.Tensor] = None
+        self.v_cache: Optional[torch.Tensor] = None
+
+    def linear_bytes(self) -> int:
+        tot = 0
+        for m in (self.qkv, self.o, self.up, self.down):
+            tot += m.qweight.numel() * 4 + m.qzeros.numel() * 4 + m.scales.numel() * 2
+        return tot
+
+
+def _rmsnorm(x, w, eps=1e-6):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class GPTQDecoder:
+    """Batch of sequences, one token per step after the prompt; greedy sampling."""
+
+    def __init__(self, cfg: DecoderConfig, batch: int = 1, device="cuda", group=None):
+        self.cfg, self.batch = cfg, batch
+        self.device = torch.device(device)
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        dev = self.device
+        self.layers = [DecoderLayer(cfg, i, self.rank, self.world, dev) for i in range(cfg.layers)]
+        g = torch.Generator(device=dev).manual_seed(7)   # replicated tensors: the same seed on every rank
+        self.embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=g, device=dev)).half()
+        self.pos_embed = None
+        if cfg.arch == "opt":
+            self.pos_embed = (0.02 * torch.randn(cfg.max_seq + 2, cfg.hidden, generator=g, device=dev)).half()
+        self.final_norm_w = torch.ones(cfg.hidden, device=dev, dtype=torch.float16)
+        self.final_norm_b = torch.zeros(cfg.hidden, device=dev, dtype=torch.float16) if cfg.arch == "opt" else None
+        vocab_pad = (cfg.vocab + self.world * 8 - 1) // (self.world * 8) * (self.world * 8)
+        self.vocab_local = vocab_pad // self.world
+        gl = torch.Generator(device=dev).manual_seed(9000 + self.rank)
+        self.lm_head = (0.02 * torch.randn(cfg.hidden, self.vocab_local, generator=gl, device=dev)).half()
+        hd = cfg.head_dim
+        for L in self.layers:
+            L.k_cache = torch.zeros(batch, L.heads_local, cfg.max_seq, hd, device=dev, dtype=torch.float16)
+            L.v_cache = torch.zeros_like(L.k_cache)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=dev).float() / hd))
+        ang = torch.arange(cfg.max_seq, device=dev).float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos().half(), ang.sin().half()
+        # device-side step state, so that a decode step can be replayed from a CUDA graph
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.tokens = torch.zeros(batch, dtype=torch.long, device=dev)
+        self.positions = torch.arange(cfg.max_seq, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+
+    # ---- pieces ----
+    def _norm(self, x, w, b):
+        if self.cfg.arch == "llama":
+            return _rmsnorm(x, w)
+        return F.layer_norm(x.float(), (x.shape[-1],), w.float(), b.float(), 1e-5).to(x.dtype)
+
+    def _all_reduce(self, t):
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def _rope(self, t, cos, sin):
+        # t: [B, H, S, hd]; cos/sin: [S, hd/2]
+        t1, t2 = t[..., 0::2], t[..., 1::2]
+        o = torch.empty_like(t)
+        o[..., 0::2] = t1 * cos - t2 * sin
+        o[..., 1::2] = t1 * sin + t2 * cos
+        return o
+
+    def _layer(self, L: DecoderLayer, x, pos_idx, S: int, decode: bool):
+        cfg = self.cfg
+        B, hd = self.batch, cfg.head_dim
+        h = self._norm(x, L.norm1_w, L.norm1_b)
+        qkv = L.qkv(h.reshape(B * S, cfg.hidden)).reshape(B, S, 3, L.heads_local, hd)
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))           # [B, H, S, hd]
+        if cfg.arch == "llama":
+            cos, sin = self.cos.index_select(0, pos_idx), self.sin.index_select(0, pos_idx)
+            q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
+        L.k_cache.index_copy_(2, pos_idx, k)
+        L.v_cache.index_copy_(2, pos_idx, v)
+        if decode:
+            mask = (self.positions <= self.pos)[None, None, None, :]          # attend to the cache up to this step
+            att = F.scaled_dot_product_attention(q, L.k_cache, L.v_cache, attn_mask=mask)
+        else:
+            att = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        att = att.transpose(1, 2).reshape(B * S, L.heads_local * hd)
+        x = x + self._all_reduce(L.o(att)).reshape(B, S, cfg.hidden)
+        h = self._norm(x, L.norm2_w, L.norm2_b)
+        u = L.up(h.reshape(B * S, cfg.hidden))
+        if cfg.arch == "llama":
+            act = F.silu(u[:, :L.inter_local]) * u[:, L.inter_local:]
+        else:
+            act = F.relu(u)
+        x = x + self._all_reduce(L.down(act.contiguous())).reshape(B, S, cfg.hidden)
+        return x
+
+    def _embed(self, tokens, pos_idx):
+        x = self.embed.index_select(0, tokens.reshape(-1)).reshape(self.batch, -1, self.cfg.hidden)
+        if self.pos_embed is not None:
+            x = x + self.pos_embed.index_select(0, pos_idx + 2)[None]
+        return x
+
+    def _sample(self, x_last):
+        h = self._norm(x_last, self.final_norm_w, self.final_norm_b)
+        logits = h @ self.lm_head                                              # [B, vocab_local]
+        val, idx = logits.float().max(dim=-1)
+        idx = idx + self.rank * self.vocab_local
+        if self.world > 1:
+            vals = [torch.empty_like(val) for _ in range(self.world)]
+            idxs = [torch.empty_like(idx) for _ in range(self.world)]
+            dist.all_gather(vals, val, group=self.group)
+            dist.all_gather(idxs, idx, group=self.group)
+            best = torch.stack(vals).argmax(dim=0)
+            idx = torch.stack(idxs).gather(0, best[None])[0]
+        return idx.clamp_(max=self.cfg.vocab - 1)
+
+    # ---- public ----
+    @torch.no_grad()
+    def prefill(self, prompt: torch.Tensor):
+        """prompt: int64 [B, S]; fills the KV cache and leaves the first generated token in self.tokens."""
+        B, S = prompt.shape
+        pos_idx = torch.arange(S, device=self.device)
+        x = self._embed(prompt, pos_idx)
+        for L in self.layers:
+            x = self._layer(L, x, pos_idx, S, decode=False)
+        self.tokens.copy_(self._sample(x[:, -1]))
+        self.pos.fill_(S)
+
+    @torch.no_grad()
+    def _decode_step(self):
+        x = self._embed(self.tokens, self.pos)
+        for L in self.layers:
+            x = self._layer(L, x, self.pos, 1, decode=True)
+        self.tokens.copy_(self._sample(x[:, -1]))
+        self.pos.add_(1)
+
+    def capture(self):
+        """Warm up (allocates scratch, builds run-time views) and capture one decode step in a CUDA graph."""
+        saved_pos, saved_tok = self.pos.clone(), self.tokens.clone()
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._decode_step()
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._decode_step()
+        self.pos.copy_(saved_pos)
+        self.tokens.copy_(saved_tok)
+
+    def decode(self, steps: int) -> torch.Tensor:
+        out = torch.empty(steps, self.batch, dtype=torch.long, device=self.device)
+        for i in range(steps):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._decode_step()
+            out[i].copy_(self.tokens)
+        return out
+
+    def bytes_per_token(self) -> int:
+        """Bytes of weights this rank streams per decode step (packed linears + its lm_head slice)."""
+        return sum(L.linear_bytes() for L in self.layers) + self.lm_head.numel() * 2

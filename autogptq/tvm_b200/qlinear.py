@@ -20,6 +20,7 @@ import torch.nn as nn
 from . import ops
 
 GEMV_MAX_M = 8
+GEMV_SPLIT_MAX_M = 24
 
 
 def _pack_fields(vals: torch.Tensor, bits: int) -> torch.Tensor:
@@ -148,9 +149,19 @@ class QuantLinear(nn.Module):
         x2 = x.half().reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        fn = ops.gemv if x2.shape[0] <= GEMV_MAX_M else ops.gemm
-        y = fn(x2, self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize,
-               bias=self.bias, x_perm=self._x_perm)
+        M = x2.shape[0]
+        kw = dict(bias=self.bias, x_perm=self._x_perm)
+        args = (self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize)
+        if M <= GEMV_MAX_M:
+            y = ops.gemv(x2, *args, **kw)
+        elif M <= GEMV_SPLIT_MAX_M:
+            # a few more rows than one GEMV takes: two or three GEMV passes (the weights of the later
+            # passes come from L2) are still cheaper than a tensor-core tile that is mostly padding
+            y = torch.empty((M, self.outfeatures), dtype=torch.float16, device=x2.device)
+            for m0 in range(0, M, GEMV_MAX_M):
+                ops.gemv(x2[m0:m0 + GEMV_MAX_M], *args, out=y[m0:m0 + GEMV_MAX_M], **kw)
+        else:
+            y = ops.gemm(x2, *args, **kw)
         return y.reshape(out_shape)
 
     def extra_repr(self):

@@ -1,0 +1,72 @@
+"""Tensor-parallel slicing rules, checked on CPU: two gloo ranks evaluate their shards with the CPU
+oracle and exchange results with the collectives the GPU path uses (all-gather for column-parallel
+outputs, all-reduce for row-parallel ones)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from autogptq.tvm_b200 import synth, tp
+from oracle import gptq_oracle as O
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _dense(layer):
+    _, _, W = O.dequantize(layer.qweight.numpy(), layer.qzeros.numpy(), layer.scales.numpy(), layer.g_idx.numpy(),
+                           layer.bits)
+    return torch.from_numpy(W.astype(np.float32))
+
+
+def _worker(rank, world, port, bits, K, N, gs):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    try:
+        full = synth.make_layer(bits, K, N, gs, False, bias=True, seed=5)     # same seed on every rank
+        x = synth.make_x(3, K, seed=2).float()
+        want = x @ _dense(full) + full.bias.float()
+        # column-parallel: concatenate the ranks' outputs
+        col = tp.shard_column(full, rank, world)
+        y_col = x @ _dense(col) + col.bias.float()
+        sizes = tp.split_sizes(N, world, 32)
+        parts = [torch.empty(3, s) for s in sizes]
+        dist.all_gather(parts, y_col) if len(set(sizes)) == 1 else None
+        if len(set(sizes)) != 1:  # uneven shards: gather through padded buffers
+            pad = torch.zeros(3, max(sizes)); pad[:, :y_col.shape[1]] = y_col
+            bufs = [torch.empty(3, max(sizes)) for _ in range(world)]
+            dist.all_gather(bufs, pad)
+            parts = [b[:, :s] for b, s in zip(bufs, sizes)]
+        assert torch.allclose(torch.cat(parts, dim=1), want, atol=1e-4)
+        # row-parallel: sum the ranks' outputs; only rank 0 carries the bias
+        row, (k_a, k_b) = tp.shard_row(full, rank, world)
+        assert (row.bias is not None) == (rank == 0)
+        y_row = x[:, k_a:k_b] @ _dense(row) + (row.bias.float() if row.bias is not None else 0.0)
+        dist.all_reduce(y_row)
+        assert torch.allclose(y_row, want, atol=1e-3)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("bits,K,N,gs", [(4, 512, 128, 128), (3, 768, 96, 128), (4, 256, 64, 64)])
+def test_two_rank_sharding_matches_the_full_layer(bits, K, N, gs):
+    mp.spawn(_worker, args=(2, _free_port(), bits, K, N, gs), nprocs=2, join=True)
+
+
+def test_split_sizes_and_errors():
+    assert tp.split_sizes(11008, 8, 128) == [1408] * 6 + [1280] * 2
+    assert sum(tp.split_sizes(4096, 8, 32)) == 4096
+    with pytest.raises(ValueError):
+        tp.split_sizes(100, 2, 32)
+    act = synth.make_layer(4, 256, 64, 64, act_order=True, seed=1)
+    with pytest.raises(ValueError):
+        tp.shard_row(act, 0, 2)

@@ -49,7 +49,7 @@ def test_two_and_more_calls_in_a_row_match_the_caller_scratch_entry_point():
 def test_capacity_is_enforced():
     cap = int(_lib.lib.b200gptq_gemv_static_capacity())
     assert cap == 4 << 20
-    bits, K, N, M = 4, 256, 65536, 8
+    bits, K, N, M = 8, 256, 262144, 8   # 8-bit layers take the general kernel, whose partial sums need M*N floats
     assert _lib.workspace_bytes(_lib.OP_GEMV, M, K, N, bits) > cap
     layer = synth.make_layer(bits, K, N, 128, False, seed=1, device=DEV)
     x = synth.make_x(M, K, seed=1, device=DEV)
