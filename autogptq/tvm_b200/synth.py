@@ -46,14 +46,14 @@ def _randint32(shape, gen, device):
 
 
 def make_layer(bits: int, K: int, N: int, group_size: int = 128, act_order: bool = False, bias: bool = False,
-               seed: int = 0, device="cpu") -> PackedLayer:
+               seed: int = 0, device="cpu", scale_mult: float = 1.0) -> PackedLayer:
     device = torch.device(device)
     gen = torch.Generator(device=device).manual_seed(seed)
     gs = group_size if group_size != -1 else K
     G = math.ceil(K / gs)
     qweight = _randint32((K // 32 * bits, N), gen, device)
     qzeros = _randint32((G, N // 32 * bits), gen, device)
-    scales = (torch.randn((G, N), generator=gen, device=device).abs() * 0.02 + 1e-3).half()
+    scales = ((torch.randn((G, N), generator=gen, device=device).abs() * 0.02 + 1e-3) * scale_mult).half()
     if act_order:
         g_idx = (torch.randperm(K, generator=gen, device=device) // gs).to(torch.int32)
     else:

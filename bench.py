@@ -39,6 +39,8 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "gemv_b3_k4096_n11008_act"
 POOL_BYTES = 320 << 20  # > 2x the 126 MB L2
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under profiles/
+NCU_DRAM_BYTES_PER_LAUNCH = {"gemv_b3_k4096_n11008_act": 17787904, "gemv_b4_k4096_n4096": None}
 METRIC = "gemv_weight_GBps"
 
 
@@ -126,6 +128,121 @@ def cpu_baseline(cfg, budget_s=20.0, max_calls=9):
             "sample": f"{len(times)} forward calls of one layer of the workload (median), torch CPU, {cores} threads"}
 
 
+def time_gemv_workload(name, dev, steps=30):
+    """Weight GB/s and roofline fraction of another GEMV workload (same method as the headline)."""
+    from autogptq.tvm_b200 import QuantLinear, ops, synth, _lib
+    cfg = WORKLOADS[name]
+    bits, K, N, gs, M = cfg["bits"], cfg["K"], cfg["N"], cfg["group_size"], cfg["M"]
+    proto = synth.make_layer(bits, K, N, gs, cfg["act_order"], seed=77, device=dev)
+    P = max(2, -(-POOL_BYTES // proto.weight_bytes()))
+    mods = []
+    for i in range(P):
+        L = proto if i == 0 else synth.make_layer(bits, K, N, gs, cfg["act_order"], seed=77 + i, device=dev)
+        m = QuantLinear(bits, gs, K, N, False)
+        m.qweight, m.qzeros, m.scales, m.g_idx = L.qweight, L.qzeros, L.scales, L.g_idx
+        m = m.to(dev)
+        m.post_init()
+        mods.append(m)
+    x = synth.make_x(M, K, seed=3, device=dev)
+    y = torch.empty((P, M, N), dtype=torch.float16, device=dev)
+    ws = ops.get_workspace(dev, _lib.workspace_bytes(_lib.OP_GEMV, M, K, N, bits))
+
+    def one_pass():
+        for i, m in enumerate(mods):
+            ops.gemv(x, m._qweight_run, m.qzeros, m.scales, m._g_idx_run, bits, gs, x_perm=m._x_perm, out=y[i],
+                     workspace=ws)
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        one_pass()
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        one_pass()
+    for _ in range(3):
+        g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (steps * P)
+    peak, _ = measured_peaks()
+    return {"workload": name, "us_per_launch": us, "weight_GBps": proto.weight_bytes() / us / 1e3,
+            "algorithmic_GBps": proto.algorithmic_bytes(M) / us / 1e3,
+            "frac_of_measured_hbm": proto.algorithmic_bytes(M) / us / 1e3 / peak, "launches": (steps + 4) * P}
+
+
+def time_gemm_sweep(dev):
+    """Config 2: 4-bit, K=4096, N=12288, M in {16,128,512,2048}; TFLOP/s against the measured dense peak."""
+    from autogptq.tvm_b200 import ops, synth
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak_tf, kind = 1590.0, "fallback"
+    if os.path.isfile(path):
+        with open(path) as f:
+            peak_tf, kind = float(json.load(f)["bf16_tflops"]), "measured"
+    K, N, bits = 4096, 12288, 4
+    layers = [synth.make_layer(bits, K, N, 128, False, seed=200 + i, device=dev) for i in range(6)]  # 151 MB > L2
+    out, launches = [], 0
+    for M in (16, 128, 512, 2048):
+        x = synth.make_x(M, K, seed=M, device=dev)
+        y = torch.empty((M, N), dtype=torch.float16, device=dev)
+        for L in layers:
+            ops.gemm(x, L.qweight, L.qzeros, L.scales, None, bits, 128, out=y)
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            for L in layers:
+                ops.gemm(x, L.qweight, L.qzeros, L.scales, None, bits, 128, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
+        tf = 2.0 * M * K * N / us / 1e6
+        launches += (reps + 1) * len(layers)
+        out.append({"M": M, "us": us, "TFLOPs": tf, "frac_of_dense_peak": tf / peak_tf,
+                    "weight_GBps": layers[0].weight_bytes() / us / 1e3})
+    return {"workload": "gemm_b4_k4096_n12288", "peak_TFLOPs": peak_tf, "peak_kind": kind, "sweep": out,
+            "launches": launches}
+
+
+def time_llama_decode(dev, world, prompt_len=512, decode_steps=256):
+    """Config 3: Llama-7B architecture, 4-bit g128, batch 1, 512-token prompt, 256 greedy decode steps, TP = world."""
+    from autogptq.tvm_b200 import decoder
+    cfg = decoder.LLAMA_7B
+    m = decoder.GPTQDecoder(cfg, batch=1, device=dev)
+    prompt = torch.randint(0, cfg.vocab, (1, prompt_len), generator=torch.Generator().manual_seed(11)).to(dev)
+    m.prefill(prompt)            # warm-up (builds run-time views, sizes scratch)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    m.prefill(prompt)
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    m.capture()
+    torch.cuda.synchronize()
+    e0.record()
+    toks = m.decode(decode_steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms, prefill_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, prefill_ms = float(t[0]), float(t[1])
+    peak, _ = measured_peaks()
+    per_tok_s = ms * 1e-3 / decode_steps
+    return {"workload": "llama7b_arch_int4_g128_bs1_p512_d256", "tp": world, "decode_tok_s": decode_steps / (ms * 1e-3),
+            "ms_per_token": ms / decode_steps, "prefill_ms": prefill_ms,
+            "weight_bytes_per_token_per_gpu": m.bytes_per_token(),
+            "frac_of_hbm_roofline": m.bytes_per_token() / per_tok_s / 1e9 / peak,
+            "last_token": int(toks[-1, 0])}
+
+
 def run_reference(args, cfg, rank):
     if rank != 0:
         return
@@ -163,6 +280,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip config 0, the GEMM sweep and the decode run")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     rank = int(os.environ.get("RANK", "0"))
@@ -262,6 +380,17 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_s = float(t[0]), float(t[1])
 
+    extras = {}
+    if not args.no_extras:
+        del mods, graph
+        torch.cuda.empty_cache()
+        if rank == 0:
+            extras["gemv_config0"] = time_gemv_workload("gemv_b4_k4096_n4096", dev)
+            extras["gemm_config2"] = time_gemm_sweep(dev)
+        torch.cuda.empty_cache()
+        barrier()
+        extras["llama7b_decode"] = time_llama_decode(dev, world)   # every rank takes part (tensor parallel)
+
     if rank == 0:
         peak, peak_kind = measured_peaks()
         ms_per_step = ms / args.steps
@@ -285,9 +414,11 @@ def main():
             "e2e": {"value": world * P * wbytes / e2e_s / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": P * M * K * 2, "d2h_bytes_per_step": P * M * N * 2,
                     "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
-            "gpu_launches": args.steps * P + e2e_steps * P,
+            "gpu_launches": args.steps * P + e2e_steps * P + sum(v.get("launches", 0) for v in extras.values()),
             "clocks": clocks,
         }
+        line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
+        line.update(extras)
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cfg)
         print(json.dumps(line))
