@@ -1,0 +1,282 @@
+// Small fused kernels for the decode step around the quantised linears: residual-add + RMSNorm /
+// LayerNorm, rotary embedding + KV-cache write, single-query attention over the cache, SwiGLU / ReLU.
+// They replace the chain of framework element-wise kernels that otherwise dominates a batch-1 decode
+// step once the linears are fast (the reference leaves these to transformers' eager modules:
+// end2end/autogptq-generation-inference-benchmark.py:26-49).  All are memory-trivial; the point is
+// launch count.  fp16 storage, fp32 arithmetic.
+#include "common.cuh"
+
+namespace b200gptq {
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// x[b,:] += add[b,:] (optional); h[b,:] = norm(x[b,:]) * w (+ beta).  rms != 0: RMSNorm, else LayerNorm.
+// One CTA of 256 threads per row; H is a multiple of 8.
+__global__ void __launch_bounds__(256)
+add_norm_kernel(__half* __restrict__ x, const __half* __restrict__ add, const __half* __restrict__ w,
+                const __half* __restrict__ beta, __half* __restrict__ h, int H, float eps, int rms) {
+    extern __shared__ float row[];  // H floats
+    __shared__ float red[2][8];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    __half* xr = x + (size_t)b * H;
+    float s = 0.f, s2 = 0.f;
+    for (int i = tid * 8; i < H; i += 256 * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+        __half2* p = reinterpret_cast<__half2*>(&v);
+        if (add) {
+            const uint4 a = *reinterpret_cast<const uint4*>(add + (size_t)b * H + i);
+            const __half2* q = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) p[k] = __hadd2(p[k], q[k]);
+            *reinterpret_cast<uint4*>(xr + i) = v;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(p[k]);
+            row[i + 2 * k] = f.x; row[i + 2 * k + 1] = f.y;
+            s += f.x + f.y; s2 += f.x * f.x + f.y * f.y;
+        }
+    }
+    s = warp_sum(s); s2 = warp_sum(s2);
+    if ((tid & 31) == 0) { red[0][tid >> 5] = s; red[1][tid >> 5] = s2; }
+    __syncthreads();
+    float ts = 0.f, ts2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { ts += red[0][k]; ts2 += red[1][k]; }
+    const float mean = rms ? 0.f : ts / H;
+    const float var = rms ? ts2 / H : fmaxf(ts2 / H - mean * mean, 0.f);
+    const float inv = rsqrtf(var + eps);
+    for (int i = tid * 8; i < H; i += 256 * 8) {
+        uint4 o;
+        __half2* po = reinterpret_cast<__half2*>(&o);
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+        const __half2* pw = reinterpret_cast<const __half2*>(&wv);
+        uint4 bv = make_uint4(0, 0, 0, 0);
+        if (beta) bv = *reinterpret_cast<const uint4*>(beta + i);
+        const __half2* pb = reinterpret_cast<const __half2*>(&bv);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 fw = __half22float2(pw[k]), fb = __half22float2(pb[k]);
+            // RMSNorm rounds the normalised value to fp16 before the weight, as the usual fp16 modules do
+            float a0 = (row[i + 2 * k] - mean) * inv, a1 = (row[i + 2 * k + 1] - mean) * inv;
+            if (rms) { a0 = __half2float(__float2half_rn(a0)); a1 = __half2float(__float2half_rn(a1)); }
+            po[k] = __floats2half2_rn(a0 * fw.x + fb.x, a1 * fw.y + fb.y);
+        }
+        *reinterpret_cast<uint4*>(h + (size_t)b * H + i) = o;
+    }
+}
+
+// qkv[b, 3, heads, hd] (one new token per sequence): rotate q and k by the angle of position `pos[0]`
+// (interleaved pairs), write q to q_out[b, heads, hd] and k, v into the caches at that position.
+// cache layout [b, heads, max_seq, hd].  rope == 0: no rotation (OPT).  One CTA per (head, b), hd/2 threads.
+__global__ void rope_cache_kernel(const __half* __restrict__ qkv, const __half* __restrict__ cos_t,
+                                  const __half* __restrict__ sin_t, const long long* __restrict__ pos,
+                                  __half* __restrict__ q_out, __half* __restrict__ k_cache,
+                                  __half* __restrict__ v_cache, int heads, int hd, int max_seq, int rope) {
+    const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x;  // pair index
+    const int p = (int)pos[0];
+    const size_t tok = (size_t)b * 3 * heads * hd;
+    const __half2 q2 = *reinterpret_cast<const __half2*>(qkv + tok + (size_t)head * hd + 2 * i);
+    const __half2 k2 = *reinterpret_cast<const __half2*>(qkv + tok + (size_t)(heads + head) * hd + 2 * i);
+    const __half2 v2 = *reinterpret_cast<const __half2*>(qkv + tok + (size_t)(2 * heads + head) * hd + 2 * i);
+    float2 q = __half22float2(q2), k = __half22float2(k2);
+    if (rope) {
+        // fp16 products and sums, like the framework expression t1*cos - t2*sin evaluated in fp16
+        const __half c = cos_t[(size_t)p * (hd / 2) + i], s = sin_t[(size_t)p * (hd / 2) + i];
+        const __half q0 = __hsub(__hmul(q2.x, c), __hmul(q2.y, s)), q1 = __hadd(__hmul(q2.x, s), __hmul(q2.y, c));
+        const __half k0 = __hsub(__hmul(k2.x, c), __hmul(k2.y, s)), k1 = __hadd(__hmul(k2.x, s), __hmul(k2.y, c));
+        q = make_float2(__half2float(q0), __half2float(q1));
+        k = make_float2(__half2float(k0), __half2float(k1));
+    }
+    *reinterpret_cast<__half2*>(q_out + ((size_t)b * heads + head) * hd + 2 * i) = __floats2half2_rn(q.x, q.y);
+    const size_t c_off = (((size_t)b * heads + head) * max_seq + p) * hd + 2 * i;
+    *reinterpret_cast<__half2*>(k_cache + c_off) = __floats2half2_rn(k.x, k.y);
+    *reinterpret_cast<__half2*>(v_cache + c_off) = v2;
+}
+
+// Single-query attention over the cache positions 0..pos[0] (inclusive).  One CTA of 8 warps per
+// (head, b); a warp takes 32 consecutive positions at a time.  Scores: each lane owns ONE position and
+// reads that key row with 128-bit loads (all 32 rows in flight together); softmax statistics once per
+// 32 positions; values: each lane owns HD/32 dims, the 32 probabilities are broadcast by shuffle and the
+// 32 value rows are read coalesced.  Online softmax per warp, combined through shared memory.
+template <int HD>
+__global__ void __launch_bounds__(256)
+attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
+                   const __half* __restrict__ v_cache, const long long* __restrict__ pos,
+                   __half* __restrict__ out, int heads, int max_seq, float scale) {
+    constexpr int PER = HD / 32, WARPS = 8;
+    __shared__ __align__(16) __half q_sm[HD];
+    __shared__ float sm_m[WARPS], sm_l[WARPS], sm_acc[WARPS][HD];
+    const int head = blockIdx.x, b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int L = (int)pos[0] + 1;
+    const size_t base = ((size_t)b * heads + head) * (size_t)max_seq * HD;
+    if (threadIdx.x < HD) q_sm[threadIdx.x] = q[((size_t)b * heads + head) * HD + threadIdx.x];
+    __syncthreads();
+    float acc[PER];
+#pragma unroll
+    for (int d = 0; d < PER; ++d) acc[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    for (int t0 = warp * 32; t0 < L; t0 += WARPS * 32) {
+        const int t = t0 + lane;
+        // ---- score of this lane's position ----
+        float dot = -INFINITY;
+        if (t < L) {
+            const uint4* kp = reinterpret_cast<const uint4*>(k_cache + base + (size_t)t * HD);
+            uint4 kv[HD / 8];
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) kv[i] = kp[i];
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                const __half2* k2 = reinterpret_cast<const __half2*>(&kv[i]);
+                const __half2* q2 = reinterpret_cast<const __half2*>(q_sm + 8 * i);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 kf = __half22float2(k2[e]), qf = __half22float2(q2[e]);
+                    s = fmaf(kf.x, qf.x, s);
+                    s = fmaf(kf.y, qf.y, s);
+                }
+            }
+            dot = s * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(dot));
+        const float pexp = (t < L) ? __expf(dot - m_new) : 0.f;
+        const float corr = __expf(m - m_new);
+        l = l * corr + warp_sum(pexp);
+        m = m_new;
+#pragma unroll
+        for (int d = 0; d < PER; ++d) acc[d] *= corr;
+        // ---- values: lanes own dims, positions are walked together ----
+        const int n = min(32, L - t0);
+        const __half* vp = v_cache + base + (size_t)t0 * HD + lane * PER;
+#pragma unroll 8
+        for (int i = 0; i < n; ++i) {
+            const float p = __shfl_sync(0xffffffffu, pexp, i);
+            if constexpr (PER == 4) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(vp + (size_t)i * HD);
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                acc[0] = fmaf(p, a.x, acc[0]); acc[1] = fmaf(p, a.y, acc[1]);
+                acc[2] = fmaf(p, c.x, acc[2]); acc[3] = fmaf(p, c.y, acc[3]);
+            } else {
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(vp + (size_t)i * HD));
+                acc[0] = fmaf(p, a.x, acc[0]); acc[1] = fmaf(p, a.y, acc[1]);
+            }
+        }
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int d = 0; d < PER; ++d) sm_acc[warp][lane * PER + d] = acc[d];
+    __syncthreads();
+    if (warp == 0) {
+        float gm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) gm = fmaxf(gm, sm_m[w]);
+        float gl = 0.f, wgt[WARPS];
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            wgt[w] = (sm_m[w] == -INFINITY) ? 0.f : __expf(sm_m[w] - gm);
+            gl += sm_l[w] * wgt[w];
+        }
+#pragma unroll
+        for (int d = 0; d < PER; ++d) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) v += sm_acc[w][lane * PER + d] * wgt[w];
+            out[((size_t)b * heads + head) * HD + lane * PER + d] = __float2half_rn(v / gl);
+        }
+    }
+}
+
+// act[b, i] = silu(u[b, i]) * u[b, I + i]  (gated != 0)   or   relu(u[b, i])  (gated == 0)
+__global__ void __launch_bounds__(256)
+act_kernel(const __half* __restrict__ u, __half* __restrict__ act, int I, int gated, size_t total) {
+    const size_t idx = ((size_t)blockIdx.x * 256 + threadIdx.x) * 2;
+    if (idx >= total) return;
+    const size_t b = idx / I, i = idx % I;
+    const size_t row = b * (size_t)(gated ? 2 * I : I);
+    const float2 g = __half22float2(*reinterpret_cast<const __half2*>(u + row + i));
+    float2 r;
+    if (gated) {
+        const float2 up = __half22float2(*reinterpret_cast<const __half2*>(u + row + I + i));
+        // silu rounded to fp16 before the product, like the framework's two element-wise kernels
+        const float s0 = __half2float(__float2half_rn(g.x / (1.f + __expf(-g.x))));
+        const float s1 = __half2float(__float2half_rn(g.y / (1.f + __expf(-g.y))));
+        r = make_float2(s0 * up.x, s1 * up.y);
+    } else {
+        r = make_float2(fmaxf(g.x, 0.f), fmaxf(g.y, 0.f));
+    }
+    *reinterpret_cast<__half2*>(act + idx) = __floats2half2_rn(r.x, r.y);
+}
+
+}  // namespace
+}  // namespace b200gptq
+
+using namespace b200gptq;
+
+extern "C" {
+
+B200GPTQ_API int b200gptq_add_norm(void* x, const void* add, const void* w, const void* beta, void* h, int rows,
+                                   int H, float eps, int rms, void* stream) {
+    if (!x || !w || !h) return B200GPTQ_ERR_NULL_POINTER;
+    if (rows <= 0 || H <= 0 || H % 8 != 0 || H > 12288) return B200GPTQ_ERR_SHAPE;
+    add_norm_kernel<<<rows, 256, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half*>(x), static_cast<const __half*>(add), static_cast<const __half*>(w),
+        static_cast<const __half*>(beta), static_cast<__half*>(h), H, eps, rms);
+    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    return B200GPTQ_OK;
+}
+
+B200GPTQ_API int b200gptq_rope_cache(const void* qkv, const void* cos_t, const void* sin_t, const void* pos,
+                                     void* q_out, void* k_cache, void* v_cache, int batch, int heads, int hd,
+                                     int max_seq, int rope, void* stream) {
+    if (!qkv || !pos || !q_out || !k_cache || !v_cache || (rope && (!cos_t || !sin_t))) return B200GPTQ_ERR_NULL_POINTER;
+    if (batch <= 0 || heads <= 0 || hd % 2 != 0 || hd > 2048) return B200GPTQ_ERR_SHAPE;
+    rope_cache_kernel<<<dim3(heads, batch), hd / 2, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(qkv), static_cast<const __half*>(cos_t), static_cast<const __half*>(sin_t),
+        static_cast<const long long*>(pos), static_cast<__half*>(q_out), static_cast<__half*>(k_cache),
+        static_cast<__half*>(v_cache), heads, hd, max_seq, rope);
+    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    return B200GPTQ_OK;
+}
+
+B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos,
+                                      void* out, int batch, int heads, int hd, int max_seq, float scale,
+                                      void* stream) {
+    if (!q || !k_cache || !v_cache || !pos || !out) return B200GPTQ_ERR_NULL_POINTER;
+    if (batch <= 0 || heads <= 0 || (hd != 64 && hd != 128)) return B200GPTQ_ERR_SHAPE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (hd == 128)
+        attn_decode_kernel<128><<<dim3(heads, batch), 256, 0, s>>>(
+            static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
+            static_cast<const long long*>(pos), static_cast<__half*>(out), heads, max_seq, scale);
+    else
+        attn_decode_kernel<64><<<dim3(heads, batch), 256, 0, s>>>(
+            static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
+            static_cast<const long long*>(pos), static_cast<__half*>(out), heads, max_seq, scale);
+    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    return B200GPTQ_OK;
+}
+
+B200GPTQ_API int b200gptq_act(const void* u, void* act, int rows, int I, int gated, void* stream) {
+    if (!u || !act) return B200GPTQ_ERR_NULL_POINTER;
+    if (rows <= 0 || I <= 0 || I % 2 != 0) return B200GPTQ_ERR_SHAPE;
+    const size_t total = (size_t)rows * I;
+    const unsigned blocks = (unsigned)((total / 2 + 255) / 256);
+    act_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(u),
+                                                                      static_cast<__half*>(act), I, gated, total);
+    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    return B200GPTQ_OK;
+}
+
+}  // extern "C"

@@ -27,7 +27,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import synth
+from . import ops, synth
 from .qlinear import QuantLinear
 
 
@@ -123,8 +123,9 @@ def _rmsnorm(x, w, eps=1e-6):
 class GPTQDecoder:
     """Batch of sequences, one token per step after the prompt; greedy sampling."""
 
-    def __init__(self, cfg: DecoderConfig, batch: int = 1, device="cuda", group=None):
+    def __init__(self, cfg: DecoderConfig, batch: int = 1, device="cuda", group=None, fused: bool = True):
         self.cfg, self.batch = cfg, batch
+        self.fused = fused and cfg.head_dim in (64, 128)   # decode steps use the fused helper kernels
         self.device = torch.device(device)
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
@@ -209,7 +210,9 @@ class GPTQDecoder:
 
     def _sample(self, x_last):
         h = self._norm(x_last, self.final_norm_w, self.final_norm_b)
-        logits = h @ self.lm_head                                              # [B, vocab_local]
+        return self._pick(h @ self.lm_head)                                    # [B, vocab_local]
+
+    def _pick(self, logits):
         val, idx = logits.float().max(dim=-1)
         idx = idx + self.rank * self.vocab_local
         if self.world > 1:
@@ -235,10 +238,38 @@ class GPTQDecoder:
 
     @torch.no_grad()
     def _decode_step(self):
+        if self.fused:
+            return self._decode_step_fused()
         x = self._embed(self.tokens, self.pos)
         for L in self.layers:
             x = self._layer(L, x, self.pos, 1, decode=True)
         self.tokens.copy_(self._sample(x[:, -1]))
+        self.pos.add_(1)
+
+    def _decode_step_fused(self):
+        """One token per sequence with the fused helper kernels: per layer 5 small launches + 4 linears."""
+        cfg, B = self.cfg, self.batch
+        hd, rms = cfg.head_dim, cfg.arch == "llama"
+        eps = 1e-6 if rms else 1e-5
+        x = self._embed(self.tokens, self.pos).reshape(B, cfg.hidden).contiguous()
+        h = torch.empty_like(x)
+        delta = None   # output of the previous row-parallel linear, added to the residual by the next norm
+        for L in self.layers:
+            ops.add_norm(x, delta, L.norm1_w, L.norm1_b, h, eps, rms)
+            qkv = L.qkv(h)
+            q = torch.empty((B, L.heads_local * hd), dtype=torch.float16, device=self.device)
+            ops.rope_cache(qkv, self.cos, self.sin, self.pos, q, L.k_cache, L.v_cache, L.heads_local, hd, rms)
+            att = torch.empty_like(q)
+            ops.attn_decode(q, L.k_cache, L.v_cache, self.pos, att, L.heads_local, hd)
+            o = self._all_reduce(L.o(att))
+            ops.add_norm(x, o, L.norm2_w, L.norm2_b, h, eps, rms)
+            u = L.up(h)
+            a = torch.empty((B, L.inter_local), dtype=torch.float16, device=self.device)
+            ops.act(u, a, L.inter_local, rms)
+            delta = self._all_reduce(L.down(a))
+        ops.add_norm(x, delta, self.final_norm_w, self.final_norm_b, h, eps, rms)
+        logits = h @ self.lm_head
+        self.tokens.copy_(self._pick(logits))
         self.pos.add_(1)
 
     def capture(self):

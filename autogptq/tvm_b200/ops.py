@@ -162,3 +162,39 @@ def gemv_static(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, b
                                            _stream(dev))
     _lib.check(st, "b200gptq_gemv_static")
     return out
+
+
+# ---- decode-step helpers (see include/b200gptq.h) -----------------------------------------------
+def add_norm(x, add, w, beta, out, eps: float, rms: bool):
+    """In place ``x += add`` (if given), then ``out = norm(x) * w (+ beta)``; x, out fp16 ``[rows, H]``."""
+    rows, H = x.shape
+    with torch.cuda.device(x.device):
+        st = _lib.lib.b200gptq_add_norm(_ptr(x), _ptr(add), _ptr(w), _ptr(beta), _ptr(out), rows, H, eps,
+                                        1 if rms else 0, _stream(x.device))
+    _lib.check(st, "b200gptq_add_norm")
+    return out
+
+
+def rope_cache(qkv, cos, sin, pos, q_out, k_cache, v_cache, heads: int, hd: int, rope: bool):
+    B, max_seq = k_cache.shape[0], k_cache.shape[2]
+    with torch.cuda.device(qkv.device):
+        st = _lib.lib.b200gptq_rope_cache(_ptr(qkv), _ptr(cos), _ptr(sin), _ptr(pos), _ptr(q_out), _ptr(k_cache),
+                                          _ptr(v_cache), B, heads, hd, max_seq, 1 if rope else 0, _stream(qkv.device))
+    _lib.check(st, "b200gptq_rope_cache")
+    return q_out
+
+
+def attn_decode(q, k_cache, v_cache, pos, out, heads: int, hd: int):
+    B, max_seq = k_cache.shape[0], k_cache.shape[2]
+    with torch.cuda.device(q.device):
+        st = _lib.lib.b200gptq_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(pos), _ptr(out), B, heads, hd,
+                                           max_seq, 1.0 / (hd ** 0.5), _stream(q.device))
+    _lib.check(st, "b200gptq_attn_decode")
+    return out
+
+
+def act(u, out, inter: int, gated: bool):
+    with torch.cuda.device(u.device):
+        st = _lib.lib.b200gptq_act(_ptr(u), _ptr(out), u.shape[0], inter, 1 if gated else 0, _stream(u.device))
+    _lib.check(st, "b200gptq_act")
+    return out

@@ -154,6 +154,29 @@ B200GPTQ_API int b200gptq_gemv_static(const void* x, const int32_t* qweight, con
 /* Bytes of the built-in scratch array used by b200gptq_gemv_static (per device). */
 B200GPTQ_API size_t b200gptq_gemv_static_capacity(void);
 
+/*
+ * Decode-step helpers around the linears (fp16 storage, fp32 arithmetic, one launch each).  The
+ * reference has no counterpart: it leaves everything between its QuantLinear calls to the
+ * transformers modules (end2end/autogptq-generation-inference-benchmark.py:26-49).  They exist so
+ * that a batch-1 decode step is a handful of launches instead of dozens of element-wise kernels.
+ *
+ *   b200gptq_add_norm     x[rows,H] += add (nullable); h = RMSNorm(x)*w (rms != 0) or LayerNorm(x)*w + beta
+ *   b200gptq_rope_cache   one new token per sequence: qkv[b,3,heads,hd] -> rotated q_out[b,heads,hd]; rotated k
+ *                         and v written at position pos[0] of the caches [b,heads,max_seq,hd]; rope == 0: no rotation
+ *   b200gptq_attn_decode  out[b,heads*hd] = softmax(q k^T * scale) v over cache positions 0..pos[0]; hd in {64,128}
+ *   b200gptq_act          act[rows,I] = silu(u[:, :I]) * u[:, I:] (gated != 0) or relu(u) (gated == 0)
+ * `pos` is a device pointer to one int64, so that a captured graph can advance it.
+ */
+B200GPTQ_API int b200gptq_add_norm(void* x, const void* add, const void* w, const void* beta, void* h, int rows,
+                                   int H, float eps, int rms, void* stream);
+B200GPTQ_API int b200gptq_rope_cache(const void* qkv, const void* cos_t, const void* sin_t, const void* pos,
+                                     void* q_out, void* k_cache, void* v_cache, int batch, int heads, int hd,
+                                     int max_seq, int rope, void* stream);
+B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos,
+                                      void* out, int batch, int heads, int hd, int max_seq, float scale,
+                                      void* stream);
+B200GPTQ_API int b200gptq_act(const void* u, void* act, int rows, int I, int gated, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

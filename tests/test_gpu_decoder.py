@@ -66,3 +66,24 @@ def test_quantised_model_matches_dense_model(arch, bits, desc_act):
     err = (xq.float() - xd.float()).abs().max().item()
     scale = xd.float().abs().max().item()
     assert err <= 2e-2 * max(scale, 1.0), (err, scale)
+
+
+@pytest.mark.parametrize("arch,bits,desc_act", [("llama", 4, False), ("opt", 3, True)])
+def test_fused_decode_step_matches_the_framework_ops(arch, bits, desc_act):
+    """The fused helper kernels (norm, rotary + cache write, single-query attention, activation) against the
+    same step written with torch ops: same residual stream, within fp16 round-off of the attention."""
+    cfg = _small(arch, bits, desc_act)
+    prompt = torch.randint(0, cfg.vocab, (2, 10), generator=torch.Generator().manual_seed(4)).to(DEV)
+    a = decoder.GPTQDecoder(cfg, batch=2, device=DEV, fused=True)
+    b = decoder.GPTQDecoder(cfg, batch=2, device=DEV, fused=False)
+    a.prefill(prompt)
+    b.prefill(prompt)
+    assert torch.equal(a.tokens, b.tokens)
+    for _ in range(4):
+        a._decode_step()
+        b._decode_step()
+    for La, Lb in zip(a.layers, b.layers):   # what the steps wrote into the caches
+        ka, kb = La.k_cache[:, :, :14].float(), Lb.k_cache[:, :, :14].float()
+        va, vb = La.v_cache[:, :, :14].float(), Lb.v_cache[:, :, :14].float()
+        assert (ka - kb).abs().max() <= 2e-2 * max(kb.abs().max().item(), 1.0)
+        assert (va - vb).abs().max() <= 2e-2 * max(vb.abs().max().item(), 1.0)
