@@ -40,7 +40,7 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "gemv_b3_k4096_n11008_act"
 POOL_BYTES = 320 << 20  # > 2x the 126 MB L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under profiles/
-NCU_DRAM_BYTES_PER_LAUNCH = {"gemv_b3_k4096_n11008_act": 17787904, "gemv_b4_k4096_n4096": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"gemv_b3_k4096_n11008_act": 20204544, "gemv_b4_k4096_n4096": None}
 METRIC = "gemv_weight_GBps"
 
 
@@ -281,6 +281,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip config 0, the GEMM sweep and the decode run")
+    ap.add_argument("--gemm-demo", type=int, default=0, metavar="M",
+                    help="only launch the config-2 GEMM a few times with M rows (a small target for ncu) and exit")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     rank = int(os.environ.get("RANK", "0"))
@@ -289,6 +291,17 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, cfg, rank)
+        return
+    if args.gemm_demo:
+        from autogptq.tvm_b200 import ops, synth
+        dev = torch.device("cuda", local_rank)
+        layers = [synth.make_layer(4, 4096, 12288, 128, False, seed=i, device=dev) for i in range(3)]
+        x = synth.make_x(args.gemm_demo, 4096, seed=1, device=dev)
+        for _ in range(2):
+            for L in layers:
+                y = ops.gemm(x, L.qweight, L.qzeros, L.scales, None, 4, 128)
+        torch.cuda.synchronize()
+        print(json.dumps({"gemm_demo_rows": args.gemm_demo, "checksum": float(y.float().abs().sum())}))
         return
 
     import torch.distributed as dist
