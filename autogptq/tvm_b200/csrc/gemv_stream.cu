@@ -12,8 +12,10 @@
 //    the previous kernel is awaited (weights are constants), so under programmatic dependent
 //    launch the next layer's weights are already landing while this layer finishes.
 //  * Unpack without shifts into place or integer->float conversion: a LOP3 masks two fields of a
-//    word and ORs in an fp16 exponent, which yields the half2 (c_lo + q_lo, c_hi + q_hi) with small
-//    known offsets c (8..128).
+//    word and ORs in an fp16 exponent, which yields the half2 (c_lo + q_lo, c_hi + q_hi) with known
+//    offsets c = 2^(10-p) for a field at bit p of its half.  Integer instructions are the scarce
+//    resource (the INT pipe issues at half the FP32 rate), so the count per weight is what is
+//    minimised: 5 per 8 weights (4-bit), 23 per 32 weights (3-bit).
 //  * The products are done by mma.sync m16n8k16 (f16 x f16 -> f32): the 16 rows of the A tile
 //    are 16 output columns, the 8 columns of B are the (up to 8) rows of x, so one instruction
 //    retires 256 weights of a warp for every M <= 8.  Offsets and zero-points are removed
@@ -21,7 +23,7 @@
 //    sum_g s * (sum_k c_k x_k + zero * sum_k x_k) -- which needs only x, scales and qzeros -- is
 //    computed once per column while the weights are in flight.
 //
-// Work split: a "unit" is 256 columns x 32 rows (4-bit) or x 128 rows (3-bit).  A thread-block
+// Work split: a "unit" is 256 columns x 128 rows of K.  A thread-block
 // cluster of up to 8 CTAs owns one 256-column group and splits its K range evenly; the CTAs'
 // partial sums are combined through distributed shared memory by the cluster's first CTA in rank
 // order (results do not depend on scheduling; no global scratch, atomics or fences are involved).
@@ -104,120 +106,125 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 
-// 3-bit: half index, inside a fragment entry, of the x value that meets field f of a row block.
-__constant__ unsigned char kSlot3[32] = {0, 2, 4, 6, 8, 1, 3, 5, 7, 9, 11, 12, 14, 16, 18, 20,
-                                         13, 15, 17, 19, 21, 23, 24, 26, 28, 30, 32, 25, 27, 29, 31, 33};
+// 3-bit: the 32 fields of a row block leave the seven-window unpack as the 16 pairs (0,3) (1,7) (2,8)
+// (4,9) (5,10) (6,11) (12,17) (13,18) (14,19) (15,20) (16,21) (22,27) (23,28) (24,29) (25,30) (26,31);
+// the x values are staged in the same order.  kSlot3[f] = half index of field f inside a fragment entry.
+__constant__ unsigned char kSlot3[32] = {0, 2, 4, 1, 6, 8, 10, 3, 5, 7, 9, 11, 12, 14, 16, 18,
+                                         20, 13, 15, 17, 19, 21, 22, 24, 26, 28, 30, 23, 25, 27, 29, 31};
+// bit position (inside its 16-bit half) at which the field of each slot is masked: offset = 2^(10 - p)
+__constant__ unsigned char kPos3[32] = {7, 0, 2, 4, 5, 7, 1, 0, 4, 3, 7, 6, 4, 3, 7, 6,
+                                        1, 0, 4, 3, 7, 6, 4, 3, 7, 6, 1, 0, 4, 3, 7, 6};
+
+// fp16 exponent pattern that turns a field at bit p of a 16-bit half into 2^(10-p) + field.
+__host__ __device__ constexpr uint32_t magic_at(int p) { return (uint32_t)(25 - p) << 10; }
 
 // ---------------------------------------------------------------------------------------
-// Per-bit-width traits.
-//   kUnitRows     rows of K covered by one unit
+// Per-bit-width traits.  A unit is 256 columns x 128 rows of K for both widths.
 //   kWordRows     word-rows of qweight per unit (= rows of the unit's ring buffer)
 //   kVecs         128-bit reads per thread per unit
-//   kBRegs        32-bit registers of B fragments per (unit, x row, quad lane), padded to x4
+//   kBRegs        32-bit registers of B fragments per (unit, x row, quad lane)
 // Lane (g = lane/4, j = lane%4) of warp w holds columns 32w + 4g .. +3 of the column group.
 // ---------------------------------------------------------------------------------------
 template <int BITS> struct Traits;
 
-// 4-bit: the quad's lane j owns word-row 4*rb + j (8 rows of K).  Fields are brought to bit 4
-// of each 16-bit half, where OR-ing 0x5400 gives 64 + q.  Pair i = (nibble i, nibble i + 4).
+// 4-bit: in each of the unit's four 32-row blocks the quad's lane j owns word-row 4*rb + j (8 rows of
+// K).  Pair i of a word is (nibble i, nibble i + 4); even pairs are masked in place (offset 1024),
+// odd pairs sit at bit 4 (offset 64); pairs 2, 3 come from the word shifted right by 8.
 template <> struct Traits<4> {
-    static constexpr int kUnitRows = 32;
-    static constexpr int kVecs = 1;
-    static constexpr int kBRegs = 4;
-
-    static constexpr int kWordRows = 4;  // word-rows of qweight per unit
-    __device__ static __forceinline__ int lane_row(int j) { return j; }   // word-row of the unit read by quad lane j
+    static constexpr int kUnitRows = 128;
+    static constexpr int kVecs = 4;
+    static constexpr int kBRegs = 16;
+    static constexpr int kWordRows = 16;
+    // ring-buffer row that holds vec r (= row block r) of quad lane j
+    __device__ static __forceinline__ int vec_row(int j, int r) { return 4 * r + j; }
 
     // d[cp] + d[2 + cp] accumulate column pair cp (columns 2cp, 2cp+1 of the lane's 4) over this unit;
     // two accumulator sets halve the length of the dependent mma chains.
-    __device__ static void compute(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm, bool has_x,
-                                   float (&d)[4][4]) {
-        uint4 bf = make_uint4(0, 0, 0, 0);
-        if (has_x) bf = *reinterpret_cast<const uint4*>(bsm);
-        const uint32_t wcol[4] = {buf[0].x, buf[0].y, buf[0].z, buf[0].w};
-        constexpr uint32_t MASK = 0x00f000f0u, MAGIC = 0x54005400u;
+    __device__ static __forceinline__ void compute(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm,
+                                                   bool has_x, float (&d)[4][4]) {
+        constexpr uint32_t MASK_E = 0x000f000fu, MAGIC_E = 0x64006400u;   // 1024 + q
+        constexpr uint32_t MASK_O = 0x00f000f0u, MAGIC_O = 0x54005400u;   //   64 + q
 #pragma unroll
-        for (int cp = 0; cp < 2; ++cp) {
-            const uint32_t wa = wcol[2 * cp], wb = wcol[2 * cp + 1];
-            const uint32_t a_p0 = lop3_and_or(wa << 4, MASK, MAGIC), b_p0 = lop3_and_or(wb << 4, MASK, MAGIC);
-            const uint32_t a_p1 = lop3_and_or(wa, MASK, MAGIC), b_p1 = lop3_and_or(wb, MASK, MAGIC);
-            const uint32_t a_p2 = lop3_and_or(wa >> 4, MASK, MAGIC), b_p2 = lop3_and_or(wb >> 4, MASK, MAGIC);
-            const uint32_t a_p3 = lop3_and_or(wa >> 8, MASK, MAGIC), b_p3 = lop3_and_or(wb >> 8, MASK, MAGIC);
-            mma16816(d[cp], a_p0, b_p0, a_p1, b_p1, bf.x, bf.y);
-            mma16816(d[2 + cp], a_p2, b_p2, a_p3, b_p3, bf.z, bf.w);  // second accumulator set: shorter chains
+        for (int rb = 0; rb < 4; ++rb) {
+            uint4 bf = make_uint4(0, 0, 0, 0);
+            if (has_x) bf = *reinterpret_cast<const uint4*>(bsm + 4 * rb);
+            const uint32_t wcol[4] = {buf[rb].x, buf[rb].y, buf[rb].z, buf[rb].w};
+#pragma unroll
+            for (int cp = 0; cp < 2; ++cp) {
+                const uint32_t wa = wcol[2 * cp], wb = wcol[2 * cp + 1];
+                const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+                mma16816(d[cp], lop3_and_or(wa, MASK_E, MAGIC_E), lop3_and_or(wb, MASK_E, MAGIC_E),
+                         lop3_and_or(wa, MASK_O, MAGIC_O), lop3_and_or(wb, MASK_O, MAGIC_O), bf.x, bf.y);
+                mma16816(d[2 + cp], lop3_and_or(wa8, MASK_E, MAGIC_E), lop3_and_or(wb8, MASK_E, MAGIC_E),
+                         lop3_and_or(wa8, MASK_O, MAGIC_O), lop3_and_or(wb8, MASK_O, MAGIC_O), bf.z, bf.w);
+            }
         }
     }
 
-    // Position (in halfs) inside a (unit, x row, quad lane) fragment entry of the x value that meets
-    // field i8 (0..7) of the lane's word: pairs are (x0,x4)(x1,x5)(x2,x6)(x3,x7).  Offset constant: 64.
-    __device__ static __forceinline__ int slot(int i8) { return 2 * (i8 & 3) + (i8 >> 2); }
-    __device__ static __forceinline__ float coef(int) { return 64.f; }
-    static constexpr int kRowsPerLane = 8;   // rows of K per quad lane and unit
+    // Where row r (0..127) of a unit goes: the quad lane that consumes it and the half index inside that
+    // lane's fragment entry.  Pairs are (x0,x4)(x1,x5)(x2,x6)(x3,x7) per row block.
+    __device__ static __forceinline__ void locate(int r, int& jl, int& h) {
+        const int rb = r >> 5, i8 = r & 7;
+        jl = (r >> 3) & 3;
+        h = 8 * rb + 2 * (i8 & 3) + (i8 >> 2);
+    }
+    __device__ static __forceinline__ float coef(int h) { return (h & 2) ? 64.f : 1024.f; }
 };
 
-// 3-bit: the quad's lane j owns row block 4*kb + j (32 rows of K = three word-rows, a 96-bit
-// stream per column).  Nine 32-bit windows of the stream each expose two clean pairs:
-// window base b (stream offset 3b - 1, so -4 for b = -1) has fields b+1 (bit 4) and b+2 (bit 7) in its low half
-// and b+6 (bit 3), b+7 (bit 6) in its high half, with exponents giving offsets 64, 8, 128, 16.
-// Fields 5, 16, 27 appear twice and field "32" does not exist: their second slot gets x = 0.
+// 3-bit: the quad's lane j owns row block 4*kb + j (32 rows of K = three word-rows, a 96-bit stream
+// per column).  Seven 32-bit windows of the stream expose the 32 fields exactly once as 16 pairs
+// (kOrder3); a field at bit p of its half gets the offset 2^(10-p).
 template <> struct Traits<3> {
     static constexpr int kUnitRows = 128;
     static constexpr int kVecs = 3;
-    static constexpr int kBRegs = 20;  // 18 used
-
+    static constexpr int kBRegs = 16;
     static constexpr int kWordRows = 12;
-    __device__ static __forceinline__ int lane_row(int j) { return 3 * j; }  // first of the 3 word-rows of quad lane j
+    __device__ static __forceinline__ int vec_row(int j, int r) { return 3 * j + r; }
 
-    // Window t (0..8) of one column's stream (w0, w1, w2); stream offsets -4, 2, 8, 29, 35, 41, 62, 68, 74.
-    template <int T_>
-    __device__ static __forceinline__ uint32_t window(uint32_t w0, uint32_t w1, uint32_t w2) {
-        if constexpr (T_ == 0) return w0 << 4;
-        else if constexpr (T_ == 1) return w0 >> 2;
-        else if constexpr (T_ == 2) return __funnelshift_r(w0, w1, 8);
-        else if constexpr (T_ == 3) return w1 << 3;
-        else if constexpr (T_ == 4) return w1 >> 3;
-        else if constexpr (T_ == 5) return __funnelshift_r(w1, w2, 9);
-        else if constexpr (T_ == 6) return w2 << 2;
-        else if constexpr (T_ == 7) return w2 >> 4;
-        else return w2 >> 10;
+    template <int PLO, int PHI>
+    __device__ static __forceinline__ uint32_t pair(uint32_t window) {
+        constexpr uint32_t mask = (7u << PLO) | (7u << (PHI + 16));
+        constexpr uint32_t magic = magic_at(PLO) | (magic_at(PHI) << 16);
+        return lop3_and_or(window, mask, magic);
     }
-
-    template <int T_>
-    __device__ static __forceinline__ void step(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm,
-                                                bool has_x, float (&d)[4][4]) {
-        constexpr uint32_t MASK_A = 0x00380070u, MAGIC_A = 0x58005400u;  // (64 + f[b+1], 128 + f[b+6])
-        constexpr uint32_t MASK_B = 0x01C00380u, MAGIC_B = 0x4C004800u;  // ( 8 + f[b+2],  16 + f[b+7])
-        uint2 bf = make_uint2(0, 0);
-        if (has_x) bf = *reinterpret_cast<const uint2*>(bsm + 2 * T_);
-        {
-            const uint32_t va = window<T_>(buf[0].x, buf[1].x, buf[2].x);
-            const uint32_t vb = window<T_>(buf[0].y, buf[1].y, buf[2].y);
-            mma16816(d[2 * (T_ & 1)], lop3_and_or(va, MASK_A, MAGIC_A), lop3_and_or(vb, MASK_A, MAGIC_A),
-                     lop3_and_or(va, MASK_B, MAGIC_B), lop3_and_or(vb, MASK_B, MAGIC_B), bf.x, bf.y);
+    // the 16 pairs of one column, in kOrder3 order
+    __device__ static __forceinline__ void unpack(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t (&p)[16]) {
+        const uint32_t v0 = w0 << 7;                        // stream offset -7
+        const uint32_t v1 = w0 >> 1;                        // 1
+        const uint32_t v2 = __funnelshift_r(w0, w1, 11);    // 11
+        const uint32_t v3 = w1;                             // 32
+        const uint32_t v4 = __funnelshift_r(w1, w2, 9);     // 41
+        const uint32_t v5 = w2 << 2;                        // 62
+        const uint32_t v6 = w2 >> 7;                        // 71
+        p[0] = pair<7, 0>(v0); p[1] = pair<2, 4>(v1); p[2] = pair<5, 7>(v1); p[3] = pair<1, 0>(v2);
+        p[4] = pair<4, 3>(v2); p[5] = pair<7, 6>(v2); p[6] = pair<4, 3>(v3); p[7] = pair<7, 6>(v3);
+        p[8] = pair<1, 0>(v4); p[9] = pair<4, 3>(v4); p[10] = pair<7, 6>(v4); p[11] = pair<4, 3>(v5);
+        p[12] = pair<7, 6>(v5); p[13] = pair<1, 0>(v6); p[14] = pair<4, 3>(v6); p[15] = pair<7, 6>(v6);
+    }
+    __device__ static __forceinline__ void compute(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm,
+                                                   bool has_x, float (&d)[4][4]) {
+        uint4 bf[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            bf[i] = make_uint4(0, 0, 0, 0);
+            if (has_x) bf[i] = *reinterpret_cast<const uint4*>(bsm + 4 * i);
         }
-        {
-            const uint32_t va = window<T_>(buf[0].z, buf[1].z, buf[2].z);
-            const uint32_t vb = window<T_>(buf[0].w, buf[1].w, buf[2].w);
-            mma16816(d[2 * (T_ & 1) + 1], lop3_and_or(va, MASK_A, MAGIC_A), lop3_and_or(vb, MASK_A, MAGIC_A),
-                     lop3_and_or(va, MASK_B, MAGIC_B), lop3_and_or(vb, MASK_B, MAGIC_B), bf.x, bf.y);
+        const uint32_t* b = reinterpret_cast<const uint32_t*>(bf);
+#pragma unroll
+        for (int cp = 0; cp < 2; ++cp) {
+            uint32_t pa[16], pb[16];
+            if (cp == 0) { unpack(buf[0].x, buf[1].x, buf[2].x, pa); unpack(buf[0].y, buf[1].y, buf[2].y, pb); }
+            else         { unpack(buf[0].z, buf[1].z, buf[2].z, pa); unpack(buf[0].w, buf[1].w, buf[2].w, pb); }
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                mma16816(d[2 * (t & 1) + cp], pa[2 * t], pb[2 * t], pa[2 * t + 1], pb[2 * t + 1], b[2 * t], b[2 * t + 1]);
         }
     }
-
-    __device__ static void compute(const uint4 (&buf)[kVecs], const uint32_t* __restrict__ bsm, bool has_x,
-                                   float (&d)[4][4]) {
-        step<0>(buf, bsm, has_x, d); step<1>(buf, bsm, has_x, d); step<2>(buf, bsm, has_x, d);
-        step<3>(buf, bsm, has_x, d); step<4>(buf, bsm, has_x, d); step<5>(buf, bsm, has_x, d);
-        step<6>(buf, bsm, has_x, d); step<7>(buf, bsm, has_x, d); step<8>(buf, bsm, has_x, d);
+    __device__ static __forceinline__ void locate(int r, int& jl, int& h) {
+        jl = r >> 5;
+        h = kSlot3[r & 31];
     }
-
-    // Half index inside a fragment entry for field f (0..31) of the lane's row block: window t,
-    // position 0..3 = (A low, A high, B low, B high) -> 4t + position.  Offsets by position: 64, 128, 8, 16.
-    __device__ static __forceinline__ int slot(int f) { return kSlot3[f]; }
-    __device__ static __forceinline__ float coef(int h) {
-        const int pos = h & 3;
-        return pos == 0 ? 64.f : pos == 1 ? 128.f : pos == 2 ? 8.f : 16.f;
-    }
-    static constexpr int kRowsPerLane = 32;
+    __device__ static __forceinline__ float coef(int h) { return (float)(1 << (10 - kPos3[h])); }
 };
 
 struct Plan {
@@ -337,7 +344,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
         const int units_per_group = group_size / UR;
         uint32_t* xs = reinterpret_cast<uint32_t*>(dsm + (size_t)R * UB);
         const int ps_pitch = max_stage_rows(M) / 8;   // ps[m * ps_pitch + octet]: (sum x, sum c*x) of 8 staged rows
-        const uint32_t lane_off = (uint32_t)(T::lane_row(j) * kRowPitch + lane_col * 4);
+        const uint32_t lane_off = (uint32_t)(lane_col * 4);
 
         for (int m = 0; m < M; ++m) corr_sm[m][tid] = 0.f;
 
@@ -405,25 +412,21 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
             auto x_consume = [&](int qi, int m0, const __half (&v)[4][4]) {
                 const bool has_q = qi < rows / 4;
                 const int kl = 4 * qi;                                // row inside the stage
-                const int ul = kl / UR, jl = (kl % UR) / T::kRowsPerLane, f0 = kl % T::kRowsPerLane;
+                const int ul = kl / UR, r_in_unit = kl % UR;
 #pragma unroll
                 for (int mm = 0; mm < 4; ++mm) {
                     const int m = m0 + mm;
                     if (m < M) {  // uniform
                         float sx = 0.f, scx = 0.f;
                         if (has_q) {
-                            __half* e = xh + (size_t)(((ul * M + m) * 4 + jl) * T::kBRegs) * 2;
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const int h = T::slot(f0 + i);
-                                e[h] = v[mm][i];
+                                int jl, h;
+                                T::locate(r_in_unit + i, jl, h);   // the four rows share jl
+                                xh[(size_t)(((ul * M + m) * 4 + jl) * T::kBRegs) * 2 + h] = v[mm][i];
                                 const float xf = __half2float(v[mm][i]);
                                 sx += xf;
                                 scx = fmaf(T::coef(h), xf, scx);
-                            }
-                            if (BITS == 3 && f0 == 0) {  // slots that no field feeds must multiply by zero
-                                const __half zero = __float2half(0.f);
-                                e[10] = zero; e[22] = zero; e[34] = zero; e[35] = zero;
                             }
                         }
                         sx += __shfl_xor_sync(0xffffffffu, sx, 1);
@@ -537,7 +540,8 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
                 uint4 cur[T::kVecs];
                 const uint8_t* src = dsm + slot * UB + lane_off;
 #pragma unroll
-                for (int r = 0; r < T::kVecs; ++r) cur[r] = *reinterpret_cast<const uint4*>(src + r * kRowPitch);
+                for (int r = 0; r < T::kVecs; ++r)
+                    cur[r] = *reinterpret_cast<const uint4*>(src + T::vec_row(j, r) * kRowPitch);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_bar(slot));  // the unit is in registers: the producer may refill the slot
                 if (++slot == R) { slot = 0; ++round; }
@@ -701,8 +705,7 @@ extern "C" __attribute__((visibility("default"))) int b200gptq_trace_clear(void)
 bool gemv_stream_supported(int M, int K, int N, int bits, int group_size) {
     (void)N;
     if (M < 1 || M > kMaxM) return false;
-    if (bits == 4) return group_size % 32 == 0 && K % 32 == 0;
-    if (bits == 3) return group_size % 128 == 0 && K % 128 == 0;
+    if (bits == 3 || bits == 4) return group_size % 128 == 0 && K % 128 == 0;
     return false;
 }
 

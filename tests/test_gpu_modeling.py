@@ -1,0 +1,36 @@
+"""from_quantized(..., use_tvm=True) end to end on a GPU: a tiny Llama checkpoint in the standard AutoGPTQ
+file layout is loaded, run through transformers' forward with the B200 QuantLinear modules, and compared
+with the same model on dense dequantised weights."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from autogptq.tvm_b200 import QuantLinear, modeling, ops
+    from test_modeling_cpu import _tiny_llama_dir
+    DEV = torch.device("cuda:0")
+
+
+def test_loaded_model_matches_dense_weights(tmp_path):
+    _tiny_llama_dir(tmp_path, bits=4, group_size=32, safetensors=True)
+    m = modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), device="cuda:0", use_safetensors=True, use_tvm=True)
+    ids = torch.randint(0, 320, (1, 24), generator=torch.Generator().manual_seed(3)).to(DEV)
+    with torch.no_grad():
+        logits_q = m.model(input_ids=ids).logits.float()          # 24 rows: the tcgen05 GEMM path
+        step_q = m.model(input_ids=ids[:, :1]).logits.float()     # 1 row: the GEMV path
+    # swap every QuantLinear for a dense layer built from the dequantise kernel's output
+    for name, mod in list(m.model.named_modules()):
+        if isinstance(mod, QuantLinear):
+            _, W = ops.dequantize(mod.qweight, mod.qzeros, mod.scales, mod.g_idx, mod.bits, mod.groupsize, want_q=False)
+            lin = torch.nn.Linear(mod.infeatures, mod.outfeatures, bias=False, device=DEV, dtype=torch.float16)
+            lin.weight.data = W.t().contiguous()
+            parent, _, leaf = name.rpartition(".")
+            setattr(m.model.get_submodule(parent), leaf, lin)
+    with torch.no_grad():
+        logits_d = m.model(input_ids=ids).logits.float()
+        step_d = m.model(input_ids=ids[:, :1]).logits.float()
+    assert (logits_q - logits_d).abs().max() <= 2e-2 * max(1.0, logits_d.abs().max().item())
+    assert (step_q - step_d).abs().max() <= 2e-2 * max(1.0, step_d.abs().max().item())
+    out = m.generate(input_ids=ids[:, :4], max_new_tokens=4, do_sample=False)
+    assert out.shape == (1, 8)
