@@ -580,8 +580,13 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
         if (n < N) {
 #pragma unroll 1
             for (int m = 0; m < M; ++m) {
+                // all remote reads are issued before the first is used; the sum stays in rank order
+                float part[8];
+#pragma unroll
+                for (int r = 1; r < 8; ++r) part[r] = (r < C) ? ld_cluster_f32(&corr_sm[m][tid], (uint32_t)r) : 0.f;
                 float v = corr_sm[m][tid];
-                for (int r = 1; r < C; ++r) v += ld_cluster_f32(&corr_sm[m][tid], (uint32_t)r);
+#pragma unroll
+                for (int r = 1; r < 8; ++r) v += part[r];
                 if (bias) v += __half2float(bias[n]);
                 y[(size_t)m * N + n] = __float2half_rn(v);
             }
