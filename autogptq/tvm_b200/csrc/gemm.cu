@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
             const int32_t* __restrict__ g_idx, const __half* __restrict__ bias, __half* __restrict__ y, int M, int K,
-            int N, int group_size, int TN, int S, unsigned int* __restrict__ status) {
+            int N, int group_size, int TN, int S, int tab_groups, unsigned int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;            // swizzled tiles need 1024-byte alignment
@@ -308,13 +308,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         const int RB = K / 32;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * quarter) << 16);
 
-        // group parameters of the row block this thread handles in the current and the next k-tile
+        // ---- scale / zero-point of (group, column) ----
+        // When they fit, the CTA's 128 columns x all groups are staged once in shared memory, packed as
+        // (fp16 scale | zero-point << 16), together with the group of every 32-row block; the producers
+        // then never wait on global memory inside the k loop.  Larger layers read them from global
+        // memory one k-tile ahead.
+        uint32_t* tab = reinterpret_cast<uint32_t*>(base_ptr + (size_t)S * stage_bytes);
+        uint16_t* gmap = reinterpret_cast<uint16_t*>(tab + (size_t)tab_groups * BN);
         auto group_of = [&](int rb) { return g_idx ? __ldg(g_idx + 32 * rb) : (32 * rb) / group_size; };
+        if (tab_groups) {
+            const int pt = threadIdx.x - 32;   // 0 .. 511
+            for (int i = pt; i < tab_groups * BN; i += kWeightWarps * kWeightGroups * 32) {
+                const int g = i / BN, c = i % BN;
+                uint32_t e = 0;
+                if (n0 + c < N) {
+                    const uint32_t sc = __half_as_ushort(scales[(size_t)g * N + n0 + c]);
+                    const uint32_t z = (uint32_t)zero_point<BITS>(qzeros + (size_t)g * zwords, n0 + c);
+                    e = sc | (z << 16);
+                }
+                tab[i] = e;
+            }
+            for (int rb = pt; rb < RB; rb += kWeightWarps * kWeightGroups * 32) gmap[rb] = (uint16_t)group_of(rb);
+            asm volatile("bar.sync 1, %0;" ::"n"(kWeightWarps * kWeightGroups * 32) : "memory");
+        }
         auto load_group = [&](int rb, int& g, __half& sc, int& z) {
             if (col_ok && rb < RB) {
-                g = group_of(rb);
-                sc = scales[(size_t)g * N + n];
-                z = zero_point<BITS>(qzeros + (size_t)g * zwords, n);
+                if (tab_groups) {
+                    g = gmap[rb];
+                    const uint32_t e = tab[g * BN + col];
+                    sc = __ushort_as_half((unsigned short)(e & 0xffffu));
+                    z = (int)(e >> 16);
+                } else {
+                    g = group_of(rb);
+                    sc = scales[(size_t)g * N + n];
+                    z = zero_point<BITS>(qzeros + (size_t)g * zwords, n);
+                }
             }
         };
         int g_cur = -1, g_nxt = -1, z_cur = 0, z_nxt = 0;
@@ -328,9 +356,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             // fetch the scale / zero-point of this thread's next k-tile now, a whole iteration ahead of their use
             constexpr int kRbStep = 2 * kWeightGroups;
             if (rb + kRbStep < RB && col_ok) {
-                const int gn = group_of(rb + kRbStep);
-                if (gn != g_cur) load_group(rb + kRbStep, g_nxt, s_nxt, z_nxt);
-                else { g_nxt = g_cur; s_nxt = s_cur; z_nxt = z_cur; }
+                if (tab_groups) {
+                    load_group(rb + kRbStep, g_nxt, s_nxt, z_nxt);
+                } else {
+                    const int gn = group_of(rb + kRbStep);
+                    if (gn != g_cur) load_group(rb + kRbStep, g_nxt, s_nxt, z_nxt);
+                    else { g_nxt = g_cur; s_nxt = s_cur; z_nxt = z_cur; }
+                }
             }
             // The TMA refilled this stage only after its previous MMAs retired (empty barrier), so the
             // A buffer of the stage in tensor memory is free as well.
@@ -422,9 +454,15 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
     if (!encode) { set_last_cuda_error((int)cudaErrorNotSupported); return B200GPTQ_ERR_CUDA; }
     const int TN = pick_tn(M);
     const int stage_bytes = TN * BK * 2 + kPackedTileBytes;
-    int S = kSmemBudget / stage_bytes;
+    // scale / zero-point table of the CTA's columns for every group, if it leaves room for >= 4 stages
+    const int gs_eff = group_size;
+    const int G = (K + gs_eff - 1) / gs_eff;
+    int tab_bytes = G * BN * 4 + ((K / 32 * 2 + 15) / 16) * 16;
+    int tab_groups = G;
+    if (G > 65535 || kSmemBudget - tab_bytes < 4 * stage_bytes) { tab_bytes = 0; tab_groups = 0; }
+    int S = (kSmemBudget - tab_bytes) / stage_bytes;
     if (S > kMaxStages) S = kMaxStages;
-    const int smem_bytes = S * stage_bytes + 1024;  // + slack to align the ring to 1024 bytes
+    const int smem_bytes = S * stage_bytes + tab_bytes + 1024;  // + slack to align the ring to 1024 bytes
 
     CUtensorMap tmap_x, tmap_w;
     const cuuint32_t estr[2] = {1, 1};
@@ -458,7 +496,7 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
     }
     dim3 grid((M + TN - 1) / TN, (N + BN - 1) / BN);
     kernel<<<grid, kGemmThreads, smem_bytes, stream>>>(tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N,
-                                                     group_size, TN, S, status);
+                                                     group_size, TN, S, tab_groups, status);
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
 }
