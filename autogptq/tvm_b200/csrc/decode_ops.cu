@@ -104,17 +104,17 @@ __global__ void rope_cache_kernel(const __half* __restrict__ qkv, const __half* 
     *reinterpret_cast<__half2*>(v_cache + c_off) = v2;
 }
 
-// Single-query attention over the cache positions 0..pos[0] (inclusive).  One CTA of 8 warps per
+// Single-query attention over the cache positions 0..pos[0] (inclusive).  One CTA of 16 warps per
 // (head, b); a warp takes 32 consecutive positions at a time.  Scores: each lane owns ONE position and
 // reads that key row with 128-bit loads (all 32 rows in flight together); softmax statistics once per
 // 32 positions; values: each lane owns HD/32 dims, the 32 probabilities are broadcast by shuffle and the
 // 32 value rows are read coalesced.  Online softmax per warp, combined through shared memory.
 template <int HD>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
                    const __half* __restrict__ v_cache, const long long* __restrict__ pos,
                    __half* __restrict__ out, int heads, int max_seq, float scale) {
-    constexpr int PER = HD / 32, WARPS = 8;
+    constexpr int PER = HD / 32, WARPS = 16;
     __shared__ __align__(16) __half q_sm[HD];
     __shared__ float sm_m[WARPS], sm_l[WARPS], sm_acc[WARPS][HD];
     const int head = blockIdx.x, b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -257,11 +257,11 @@ B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const 
     if (batch <= 0 || heads <= 0 || (hd != 64 && hd != 128)) return B200GPTQ_ERR_SHAPE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (hd == 128)
-        attn_decode_kernel<128><<<dim3(heads, batch), 256, 0, s>>>(
+        attn_decode_kernel<128><<<dim3(heads, batch), 512, 0, s>>>(
             static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
             static_cast<const long long*>(pos), static_cast<__half*>(out), heads, max_seq, scale);
     else
-        attn_decode_kernel<64><<<dim3(heads, batch), 256, 0, s>>>(
+        attn_decode_kernel<64><<<dim3(heads, batch), 512, 0, s>>>(
             static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
             static_cast<const long long*>(pos), static_cast<__half*>(out), heads, max_seq, scale);
     B200GPTQ_CUDA_TRY(cudaGetLastError());
