@@ -104,11 +104,26 @@ __global__ void rope_cache_kernel(const __half* __restrict__ qkv, const __half* 
     *reinterpret_cast<__half2*>(v_cache + c_off) = v2;
 }
 
-// Single-query attention over the cache positions 0..pos[0] (inclusive).  One CTA of 16 warps per
-// (head, b); a warp takes 32 consecutive positions at a time.  Scores: each lane owns ONE position and
-// reads that key row with 128-bit loads (all 32 rows in flight together); softmax statistics once per
+__device__ __forceinline__ float ld_cluster_f32(const float* local_ptr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local_ptr)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Single-query attention over the cache positions 0..pos[0] (inclusive).  A cluster of kAttnSplit CTAs
+// of 16 warps serves one (head, b); the 32-position chunks are dealt round-robin to all warps of the
+// cluster, so a prompt of ~2000 tokens is still one chunk per warp.  Scores: each lane owns ONE position
+// and reads that key row with 128-bit loads (all 32 rows in flight together); softmax statistics once per
 // 32 positions; values: each lane owns HD/32 dims, the 32 probabilities are broadcast by shuffle and the
-// 32 value rows are read coalesced.  Online softmax per warp, combined through shared memory.
+// 32 value rows are read coalesced.  Online softmax per warp; warps are combined through shared memory
+// and the CTAs of the cluster through distributed shared memory by the cluster's first CTA.
+constexpr int kAttnSplit = 4;
 template <int HD>
 __global__ void __launch_bounds__(512)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
@@ -117,7 +132,9 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
     constexpr int PER = HD / 32, WARPS = 16;
     __shared__ __align__(16) __half q_sm[HD];
     __shared__ float sm_m[WARPS], sm_l[WARPS], sm_acc[WARPS][HD];
-    const int head = blockIdx.x, b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float cta_m, cta_l, cta_acc[HD];   // this CTA's partial result, read by the cluster's first CTA
+    const int split = blockIdx.x % kAttnSplit, head = blockIdx.x / kAttnSplit, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int L = (int)pos[0] + 1;
     const size_t base = ((size_t)b * heads + head) * (size_t)max_seq * HD;
     if (threadIdx.x < HD) q_sm[threadIdx.x] = q[((size_t)b * heads + head) * HD + threadIdx.x];
@@ -126,7 +143,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
 #pragma unroll
     for (int d = 0; d < PER; ++d) acc[d] = 0.f;
     float m = -INFINITY, l = 0.f;
-    for (int t0 = warp * 32; t0 < L; t0 += WARPS * 32) {
+    for (int t0 = (warp * kAttnSplit + split) * 32; t0 < L; t0 += WARPS * kAttnSplit * 32) {
         const int t = t0 + lane;
         // ---- score of this lane's position ----
         float dot = -INFINITY;
@@ -178,7 +195,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
 #pragma unroll
     for (int d = 0; d < PER; ++d) sm_acc[warp][lane * PER + d] = acc[d];
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 0) {   // combine the 16 warps of this CTA
         float gm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) gm = fmaxf(gm, sm_m[w]);
@@ -188,14 +205,43 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
             wgt[w] = (sm_m[w] == -INFINITY) ? 0.f : __expf(sm_m[w] - gm);
             gl += sm_l[w] * wgt[w];
         }
+        if (lane == 0) { cta_m = gm; cta_l = gl; }
 #pragma unroll
         for (int d = 0; d < PER; ++d) {
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) v += sm_acc[w][lane * PER + d] * wgt[w];
+            cta_acc[lane * PER + d] = v;
+        }
+    }
+    cluster_sync_all();   // every CTA's (cta_m, cta_l, cta_acc) is visible to the cluster
+    if (split == 0 && warp == 0) {
+        float pm[kAttnSplit], pl[kAttnSplit], pa[kAttnSplit][PER];
+#pragma unroll
+        for (int r = 0; r < kAttnSplit; ++r) {   // all remote reads in flight together
+            pm[r] = ld_cluster_f32(&cta_m, r);
+            pl[r] = ld_cluster_f32(&cta_l, r);
+#pragma unroll
+            for (int d = 0; d < PER; ++d) pa[r][d] = ld_cluster_f32(&cta_acc[lane * PER + d], r);
+        }
+        float gm = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < kAttnSplit; ++r) gm = fmaxf(gm, pm[r]);
+        float gl = 0.f, wgt[kAttnSplit];
+#pragma unroll
+        for (int r = 0; r < kAttnSplit; ++r) {
+            wgt[r] = (pm[r] == -INFINITY) ? 0.f : __expf(pm[r] - gm);
+            gl += pl[r] * wgt[r];
+        }
+#pragma unroll
+        for (int d = 0; d < PER; ++d) {
+            float v = 0.f;
+#pragma unroll
+            for (int r = 0; r < kAttnSplit; ++r) v += pa[r][d] * wgt[r];
             out[((size_t)b * heads + head) * HD + lane * PER + d] = __float2half_rn(v / gl);
         }
     }
+    cluster_sync_all();   // keep every CTA's shared memory alive until it has been read
 }
 
 // act[b, i] = silu(u[b, i]) * u[b, I + i]  (gated != 0)   or   relu(u[b, i])  (gated == 0)
@@ -255,15 +301,28 @@ B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const 
                                       void* stream) {
     if (!q || !k_cache || !v_cache || !pos || !out) return B200GPTQ_ERR_NULL_POINTER;
     if (batch <= 0 || heads <= 0 || (hd != 64 && hd != 128)) return B200GPTQ_ERR_SHAPE;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (hd == 128)
-        attn_decode_kernel<128><<<dim3(heads, batch), 512, 0, s>>>(
-            static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
-            static_cast<const long long*>(pos), static_cast<__half*>(out), heads, max_seq, scale);
-    else
-        attn_decode_kernel<64><<<dim3(heads, batch), 512, 0, s>>>(
-            static_cast<const __half*>(q), static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache),
-            static_cast<const long long*>(pos), static_cast<__half*>(out), heads, max_seq, scale);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(heads * kAttnSplit, batch);
+    cfg.blockDim = dim3(512);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kAttnSplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const __half* qh = static_cast<const __half*>(q);
+    const __half* kh = static_cast<const __half*>(k_cache);
+    const __half* vh = static_cast<const __half*>(v_cache);
+    const long long* ph = static_cast<const long long*>(pos);
+    __half* oh = static_cast<__half*>(out);
+    if (hd == 128) {
+        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, qh, kh, vh, ph, oh, heads, max_seq, scale));
+    } else {
+        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, qh, kh, vh, ph, oh, heads, max_seq, scale));
+    }
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
 }
