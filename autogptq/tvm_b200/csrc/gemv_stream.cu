@@ -233,12 +233,13 @@ struct Plan {
     int cluster;      // CTAs per cluster: the column group's K range is split evenly among them
     int stage_units;  // units whose x values are staged in shared memory at a time
     int ring_units;   // unit buffers in the shared-memory ring
+    int push;         // 1: the K slices are combined by pushing partial sums into the first CTA's shared memory
 };
 
 // Rows of x staged at a time: the whole K slice of a CTA for the usual decode shapes.
 __host__ __device__ inline int max_stage_rows(int M) { return M <= 2 ? kMaxStageRows : (M <= 4 ? 1024 : 512); }
 
-// Dynamic shared memory, in this order: ring | xs | s_sm | z_sm | corr_sm | ps
+// Dynamic shared memory, in this order: ring | xs | s_sm | z_sm | corr_sm | ps | red
 template <int BITS> __host__ __device__ constexpr int unit_bytes() { return Traits<BITS>::kWordRows * kRowPitch; }
 template <int BITS> __host__ __device__ inline int xs_bytes(int M) {
     return (max_stage_rows(M) / Traits<BITS>::kUnitRows) * M * 4 * Traits<BITS>::kBRegs * 4;
@@ -247,7 +248,21 @@ __host__ __device__ inline int s_sm_bytes() { return kStageGroups * kCgCols * 4;
 __host__ __device__ inline int z_sm_bytes() { return kStageGroups * kCgCols * 4; }
 __host__ __device__ inline int corr_bytes(int M) { return M * kCgCols * 4; }
 __host__ __device__ inline int ps_bytes(int M) { return M * (max_stage_rows(M) / 8) * 8; }
+// landing zone of the other CTAs' partial sums (push combine): red[rank - 1][m][column]
+__host__ __device__ inline int red_bytes(int M, int cluster) { return (cluster - 1) * M * kCgCols * 4; }
+constexpr int kMaxRedBytes = 16 * 1024;   // larger combines read the partial sums remotely instead
 
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Asynchronous store of a float into the shared memory of CTA `rank` of this cluster, at the offset of
+// `local_ptr`; the 4 bytes are counted on that CTA's mbarrier at the offset of `local_bar`.
+__device__ __forceinline__ void st_async_cluster_f32(const float* local_ptr, uint32_t local_bar, uint32_t rank, float v) {
+    uint32_t dst, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(smem_u32(local_ptr)), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(local_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+                 ::"r"(dst), "f"(v), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -287,7 +302,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     constexpr int UB = unit_bytes<BITS>();
 
     extern __shared__ __align__(128) uint8_t dsm[];
-    __shared__ __align__(8) uint64_t bars[2 * kMaxRing];   // full[R], empty[R]
+    __shared__ __align__(8) uint64_t bars[2 * kMaxRing + 1];   // full[R], empty[R], red
     __shared__ float t_x[kStageGroups * kMaxM], t_cx[kStageGroups * kMaxM];
     __shared__ volatile int gave_up;
 
@@ -308,6 +323,12 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     float (*z_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs + s_sm_bytes());
     float (*corr_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs + s_sm_bytes() + z_sm_bytes());
     float2* ps = reinterpret_cast<float2*>(after_xs + s_sm_bytes() + z_sm_bytes() + corr_bytes(M));
+    // (computed where they are used, to keep them out of registers during the main loop)
+    auto red_ptr = [&]() {
+        return reinterpret_cast<float*>(dsm + (size_t)plan.ring_units * UB + xs_bytes<BITS>(M) + s_sm_bytes() +
+                                        z_sm_bytes() + corr_bytes(M) + ps_bytes(M));
+    };
+    auto red_bar_addr = [&]() { return smem_u32(bars) + 8u * (2 * kMaxRing); };
 
     if (tid == 0) {
         gave_up = 0;
@@ -315,9 +336,13 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
             mbar_init(full_bar(s), 1);                 // the producer's expect_tx arrive
             mbar_init(empty_bar(s), kConsumerWarps);   // one arrive per consumer warp
         }
+        mbar_init(red_bar_addr(), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first CTA of the cluster expects one float per (other CTA, x row, column)
+        if (plan.push && rank == 0) mbar_arrive_expect_tx(red_bar_addr(), (uint32_t)red_bytes(M, C));
     }
     __syncthreads();
+    if (plan.push) cluster_arrive();   // matched by the wait in front of the first store into another CTA
 
     if (warp == kConsumerWarps) {
         // ===== producer warp: stream this CTA's units into the ring =====
@@ -336,6 +361,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
             }
             if (++slot == R) { slot = 0; ++round; }
         }
+        if (plan.push) cluster_wait();
     } else {
         // ===== consumer warps =====
         const int g = lane >> 2, j = lane & 3;
@@ -561,15 +587,47 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
 
         // ---- this CTA's partial result: combine the lanes, remove the offset / zero-point term ----
         consumer_sync();  // corr_sm is complete
+        const bool push = plan.push != 0;
+        if (push) cluster_wait();   // every CTA of the cluster is running and has initialised its barriers
+        float* red = red_ptr();
+        const uint32_t red_bar = red_bar_addr();
 #pragma unroll
         for (int cp = 0; cp < 2; ++cp)
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const int m = 2 * j + (r & 1);
                 const int c = lane_col + 2 * cp + (r >> 1);
-                if (m < M) corr_sm[m][c] = out[cp][r] - corr_sm[m][c];
+                if (m < M) {
+                    const float v = out[cp][r] - corr_sm[m][c];
+                    if (push && rank > 0) st_async_cluster_f32(red + ((rank - 1) * M + m) * kCgCols + c, red_bar, 0u, v);
+                    else corr_sm[m][c] = v;
+                }
             }
         consumer_sync();
+    }
+
+    if (plan.push) {
+        float* red = red_ptr();
+        const uint32_t red_bar = red_bar_addr();
+        // ---- push combine: the other CTAs are done once their stores are issued (nothing reads their shared
+        //      memory); the first CTA waits for all of them on its barrier and adds them up in rank order ----
+        TRACE(6);
+        if (rank == 0 && warp < kConsumerWarps) {
+            mbar_wait(red_bar, 0, &gave_up);
+            const int n = cg * kCgCols + tid;
+            if (n < N) {
+#pragma unroll 1
+                for (int m = 0; m < M; ++m) {
+                    float v = corr_sm[m][tid];
+                    for (int r = 1; r < C; ++r) v += red[((r - 1) * M + m) * kCgCols + tid];
+                    if (bias) v += __half2float(bias[n]);
+                    y[(size_t)m * N + n] = __float2half_rn(v);
+                }
+            }
+        }
+        if (tid == 0 && gave_up) atomicExch(status + kStatusWord, 1u);
+        TRACE(7);
+        return;
     }
 
     // ---- combine the K slices of the cluster through distributed shared memory, in rank order ----
@@ -641,7 +699,12 @@ Plan make_plan(int M, int K, int N, int group_size, int* smem_bytes) {
     if (ring > kMaxRing) ring = kMaxRing;
     if (ring < 2) ring = 2;
     p.ring_units = ring;
-    *smem_bytes = ring * unit_bytes<BITS>() + other;
+    static const bool push_env = [] {
+        const char* e = std::getenv("B200GPTQ_GEMV_PUSH");
+        return !(e && e[0] == '0');
+    }();
+    p.push = (c > 1 && push_env && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
+    *smem_bytes = ring * unit_bytes<BITS>() + other + (p.push ? red_bytes(M, c) : 0);
     return p;
 }
 
