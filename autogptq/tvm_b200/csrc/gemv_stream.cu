@@ -6,11 +6,13 @@
 // (about two instructions per weight are available at full bandwidth), and a single layer lasts
 // only a few microseconds, so three things shape it:
 //
-//  * Weight stream: a producer warp copies the CTA's share of qweight into a shared-memory ring
-//    with bulk asynchronous copies (cp.async.bulk, one per 1 KB row segment, completion counted
-//    on an mbarrier).  It starts at the first instruction of the kernel, before the dependency on
-//    the previous kernel is awaited (weights are constants), so under programmatic dependent
-//    launch the next layer's weights are already landing while this layer finishes.
+//  * Weight stream: qweight reaches shared memory through a ring of "units" filled by TMA, one
+//    cp.async.bulk.tensor box per unit (12 or 16 KB, completion counted on an mbarrier).  Measured on
+//    B200: 1 KB bulk copies cap a CTA's stream at ~25 GB/s however many are in flight, one box per unit
+//    streams at the full 5.6 TB/s from 148 CTAs.  The box is laid out with the 128-byte swizzle so the
+//    quad lanes' 128-bit reads of different word-rows fall into different banks.  The ring is filled at
+//    the start of the kernel, before the dependency on the previous kernel is awaited (weights are
+//    constants), and every warp counts itself in when it has read a unit: the last one refills the slot.
 //  * Unpack without shifts into place or integer->float conversion: a LOP3 masks two fields of a
 //    word and ORs in an fp16 exponent, which yields the half2 (c_lo + q_lo, c_hi + q_hi) with known
 //    offsets c = 2^(10-p) for a field at bit p of its half.  Integer instructions are the scarce
@@ -23,16 +25,19 @@
 //    sum_g s * (sum_k c_k x_k + zero * sum_k x_k) -- which needs only x, scales and qzeros -- is
 //    computed once per column while the weights are in flight.
 //
-// Work split: a "unit" is 256 columns x 128 rows of K.  A thread-block
-// cluster of up to 8 CTAs owns one 256-column group and splits its K range evenly; the CTAs'
-// partial sums are combined through distributed shared memory by the cluster's first CTA in rank
-// order (results do not depend on scheduling; no global scratch, atomics or fences are involved).
+// Work split: a "unit" is 256 columns x 128 rows of K.  A CTA is 8 warps (128 registers per thread, two
+// CTAs per SM).  A thread-block cluster of up to 8 CTAs owns one 256-column group and splits its K range
+// evenly; the CTAs' partial sums are combined in the cluster's first CTA in rank order, either pushed
+// there with asynchronous shared-memory stores (small M) or read from it through distributed shared memory
+// (results do not depend on scheduling; no global scratch, atomics or fences are involved).
 // The cluster size is the largest that still lets every CTA of the grid be resident at once.
 // Every mbarrier wait is bounded; if one expires the kernel raises a sticky status word and runs
 // on without waiting.
 //
 // Reference semantics: auto_gptq/nn_modules/qlinear.py:197-243; the kernel this replaces is
 // the TVM-generated SIMT GEMV src/kernels/gemv_kernel.cu:25-55.
+#include <cuda.h>
+
 #include <cstdlib>
 
 #include "common.cuh"
@@ -43,14 +48,14 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = 32 * kConsumerWarps;   // 256
-constexpr int kThreads = kConsumerThreads + 32;          // + the producer warp
+constexpr int kThreads = kConsumerThreads;               // warp 0 also issues the weight copies
 constexpr int kCgCols = 32 * kConsumerWarps;             // 256 columns per column group
 constexpr int kMaxM = 8;
 constexpr int kMaxStageRows = 2048;         // rows of x staged in shared memory at a time (fewer when M is large)
 constexpr int kStageGroups = 16;            // and at most this many groups
-constexpr int kInflightBytes = 40 * 1024;   // weight bytes a CTA keeps in flight when two CTAs share an SM (measured:
-                                            // deeper rings push a CTA past half an SM and cost more than they gain)
-constexpr int kRowPitch = kCgCols * 4 + 32; // bytes between word-rows in the ring: conflict-free 128-bit reads
+constexpr int kSmemBudget = 107 * 1024;     // dynamic shared memory of a CTA: just under half an SM, so that two CTAs
+                                            // are resident on an SM at the same time
+constexpr int kRowPitch = kCgCols * 4;      // bytes of one word-row of a unit
 constexpr int kMaxRing = 32;
 constexpr int kStatusWord = kMaxCounters - 1;
 
@@ -72,9 +77,6 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -99,10 +101,14 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (clock64() - t0 > 1000000000LL) *gave_up = 1;
     }
 }
-// Bulk asynchronous copy global -> shared memory of this CTA; both addresses and the size are multiples of 16.
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+// One TMA copy of a 3-D box into shared memory of this CTA.  qweight is described to the TMA unit as
+// [N/32 column chunks][word-rows][32 columns]; a box is 8 chunks x the unit's word-rows x 32 columns and lands as
+// [chunk][word-row][128 bytes] with the 128-byte swizzle (16-byte piece p of line L sits at piece p ^ (L & 7)),
+// which is what lets the four lanes of a quad read different word-rows of the same columns without bank conflicts.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 
@@ -127,16 +133,17 @@ __host__ __device__ constexpr uint32_t magic_at(int p) { return (uint32_t)(25 - 
 // ---------------------------------------------------------------------------------------
 template <int BITS> struct Traits;
 
-// 4-bit: in each of the unit's four 32-row blocks the quad's lane j owns word-row 4*rb + j (8 rows of
-// K).  Pair i of a word is (nibble i, nibble i + 4); even pairs are masked in place (offset 1024),
-// odd pairs sit at bit 4 (offset 64); pairs 2, 3 come from the word shifted right by 8.
+// 4-bit: the quad's lane j owns word-rows 2j, 2j+1, 8+2j, 9+2j of the unit's 16 (8 rows of K each): with the
+// swizzled ring layout the four lanes of a quad then read from different banks.  Pair i of a word is
+// (nibble i, nibble i + 4); even pairs are masked in place (offset 1024), odd pairs sit at bit 4 (offset 64);
+// pairs 2, 3 come from the word shifted right by 8.
 template <> struct Traits<4> {
     static constexpr int kUnitRows = 128;
     static constexpr int kVecs = 4;
     static constexpr int kBRegs = 16;
     static constexpr int kWordRows = 16;
-    // ring-buffer row that holds vec r (= row block r) of quad lane j
-    __device__ static __forceinline__ int vec_row(int j, int r) { return 4 * r + j; }
+    // word-row of the unit that holds vec r of quad lane j
+    __device__ static __forceinline__ int vec_row(int j, int r) { return 2 * j + (r & 1) + 8 * (r >> 1); }
 
     // d[cp] + d[2 + cp] accumulate column pair cp (columns 2cp, 2cp+1 of the lane's 4) over this unit;
     // two accumulator sets halve the length of the dependent mma chains.
@@ -164,8 +171,9 @@ template <> struct Traits<4> {
     // Where row r (0..127) of a unit goes: the quad lane that consumes it and the half index inside that
     // lane's fragment entry.  Pairs are (x0,x4)(x1,x5)(x2,x6)(x3,x7) per row block.
     __device__ static __forceinline__ void locate(int r, int& jl, int& h) {
-        const int rb = r >> 5, i8 = r & 7;
-        jl = (r >> 3) & 3;
+        const int wr = r >> 3, i8 = r & 7;             // word-row of the unit, row inside the word
+        jl = (wr & 7) >> 1;
+        const int rb = (wr & 1) + 2 * (wr >> 3);        // which of the lane's four vecs
         h = 8 * rb + 2 * (i8 & 3) + (i8 >> 2);
     }
     __device__ static __forceinline__ float coef(int h) { return (h & 2) ? 64.f : 1024.f; }
@@ -276,24 +284,64 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local_ptr, uint32_t
 }
 
 #ifdef B200GPTQ_TRACE
-__device__ unsigned long long g_trace[1024 * 8];
-__device__ __forceinline__ void trace_mark(int slot) {
+// Timeline recorder for experiments (never compiled into the library that ships): every CTA takes a
+// ticket and records a tag (the weight pointer, i.e. the launch) plus the global timer at up to 8 marks.
+constexpr int kTraceSlots = 8192;
+__device__ unsigned long long g_trace[kTraceSlots * 10];
+__device__ unsigned int g_ticket;
+__device__ __forceinline__ void trace_mark(int slot, const void* tag = nullptr) {
+    __shared__ unsigned int s_ticket;
     if (threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        if (g_trace[blockIdx.x * 8 + slot] == 0) g_trace[blockIdx.x * 8 + slot] = t;
+        if (slot == 0) {
+            s_ticket = atomicAdd(&g_ticket, 1u);
+            if (s_ticket < kTraceSlots) {
+                unsigned int smid;
+                asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+                g_trace[s_ticket * 10 + 9] = (unsigned long long)(blockIdx.x + 1) | ((unsigned long long)smid << 32);
+                g_trace[s_ticket * 10 + 8] = (unsigned long long)tag;
+            }
+        }
+        if (s_ticket < kTraceSlots) g_trace[s_ticket * 10 + slot] = t;
     }
 }
-__global__ void trace_clear_kernel() { g_trace[blockIdx.x * blockDim.x + threadIdx.x] = 0; }
+__global__ void trace_clear_kernel() {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < kTraceSlots * 10) g_trace[i] = 0;
+    if (i == 0) g_ticket = 0;
+}
+__device__ unsigned long long g_trace_units[8 * 64];
+__device__ __forceinline__ void trace_unit(int blk, int i) {
+    if ((threadIdx.x & 31) == 0 && (blockIdx.x == blk) && i < 64) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_trace_units[(threadIdx.x >> 5) * 64 + i] = t;
+    }
+}
+#define TRACE_UNIT(i)
+#define CLK_DECL long long c_wait = 0, c_load = 0, c_comp = 0, c_flush = 0, c_stage = 0, c_t
+#define CLK_START c_t = clock64()
+#define CLK_ADD(acc) do { const long long c_n = clock64(); acc += c_n - c_t; c_t = c_n; } while (0)
+#define CLK_STORE do { if ((threadIdx.x & 31) == 0 && blockIdx.x == 35) { unsigned long long* o = g_trace_units + (threadIdx.x >> 5) * 64; \
+    o[0] = c_wait; o[1] = c_load; o[2] = c_comp; o[3] = c_flush; o[4] = c_stage; } } while (0)
 #define TRACE(slot) trace_mark(slot)
+#define TRACE0(tag) trace_mark(0, tag)
 #else
 #define TRACE(slot)
+#define TRACE0(tag)
+#define TRACE_UNIT(i)
+#define CLK_DECL
+#define CLK_START
+#define CLK_ADD(acc)
+#define CLK_STORE
 #endif
 
 // One cluster per column group; CTA `rank` of the cluster owns units [rank*kbs/C, (rank+1)*kbs/C).
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
-gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qweight,
+gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __restrict__ x,
+                   const int32_t* __restrict__ qweight,
                    const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
                    const int32_t* __restrict__ x_perm, const __half* __restrict__ bias, __half* __restrict__ y,
                    int M, int K, int N, int group_size, Plan plan, unsigned int* __restrict__ status) {
@@ -302,13 +350,12 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     constexpr int UB = unit_bytes<BITS>();
 
     extern __shared__ __align__(128) uint8_t dsm[];
-    __shared__ __align__(8) uint64_t bars[2 * kMaxRing + 1];   // full[R], empty[R], red
+    __shared__ __align__(8) uint64_t bars[2 * kMaxRing + 1];   // full[R] at 0, red at 2 * kMaxRing
     __shared__ float t_x[kStageGroups * kMaxM], t_cx[kStageGroups * kMaxM];
     __shared__ volatile int gave_up;
+    __shared__ unsigned int taken[kMaxRing];   // warps that have moved the unit in a ring slot to registers
 
-    // Let the next kernel of the stream start its own weight stream as early as possible.
-    asm volatile("griddepcontrol.launch_dependents;");
-    TRACE(0);
+    TRACE0(qweight);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int R = plan.ring_units, C = plan.cluster, kbs = plan.kbs;
@@ -316,25 +363,26 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     const int kb_begin = (int)(((long long)rank * kbs) / C), kb_end = (int)(((long long)(rank + 1) * kbs) / C);
     const uint32_t bar_base = smem_u32(bars);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxRing + s); };
 
-    uint8_t* after_xs = dsm + (size_t)R * UB + xs_bytes<BITS>(M);
+    // the swizzle pattern is a function of the address: the ring starts on a 1024-byte boundary
+    uint8_t* ring = dsm + ((1024u - (smem_u32(dsm) & 1023u)) & 1023u);
+    uint8_t* after_xs = ring + (size_t)R * UB + xs_bytes<BITS>(M);
     float (*s_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs);
     float (*z_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs + s_sm_bytes());
     float (*corr_sm)[kCgCols] = reinterpret_cast<float (*)[kCgCols]>(after_xs + s_sm_bytes() + z_sm_bytes());
     float2* ps = reinterpret_cast<float2*>(after_xs + s_sm_bytes() + z_sm_bytes() + corr_bytes(M));
     // (computed where they are used, to keep them out of registers during the main loop)
     auto red_ptr = [&]() {
-        return reinterpret_cast<float*>(dsm + (size_t)plan.ring_units * UB + xs_bytes<BITS>(M) + s_sm_bytes() +
+        return reinterpret_cast<float*>(ring + (size_t)plan.ring_units * UB + xs_bytes<BITS>(M) + s_sm_bytes() +
                                         z_sm_bytes() + corr_bytes(M) + ps_bytes(M));
     };
     auto red_bar_addr = [&]() { return smem_u32(bars) + 8u * (2 * kMaxRing); };
 
+    if (tid < kMaxRing) taken[tid] = 0u;
     if (tid == 0) {
         gave_up = 0;
         for (int s = 0; s < R; ++s) {
-            mbar_init(full_bar(s), 1);                 // the producer's expect_tx arrive
-            mbar_init(empty_bar(s), kConsumerWarps);   // one arrive per consumer warp
+            mbar_init(full_bar(s), 1);                 // the expect_tx arrive of the lane that issues the copies
         }
         mbar_init(red_bar_addr(), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -344,33 +392,32 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     __syncthreads();
     if (plan.push) cluster_arrive();   // matched by the wait in front of the first store into another CTA
 
-    if (warp == kConsumerWarps) {
-        // ===== producer warp: stream this CTA's units into the ring =====
-        int slot = 0, round = 0;
-        const int cols = min(kCgCols, N - cg * kCgCols);
-        const uint32_t row_bytes = (uint32_t)cols * 4u;
-        // start once the consumers have queued their first small loads (scales, zero-points)
-        asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-            if (round > 0) mbar_wait(empty_bar(slot), (round - 1) & 1, &gave_up);
-            if (lane == 0) mbar_arrive_expect_tx(full_bar(slot), row_bytes * T::kWordRows);
-            __syncwarp();
-            if (lane < T::kWordRows) {
-                const int32_t* src = qweight + (size_t)(kb * T::kWordRows + lane) * N + (size_t)cg * kCgCols;
-                bulk_copy_g2s(smem_u32(dsm) + slot * UB + lane * kRowPitch, src, row_bytes, full_bar(slot));
-            }
-            if (++slot == R) { slot = 0; ++round; }
+    // Copy unit `kb` of this CTA's column group into ring slot `slot`: one TMA box of kWordRows x 256 words
+    // (columns past N are filled with zeros and count towards the expected bytes like the rest).
+    auto issue_unit = [&](int kb, int slot) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(full_bar(slot), (uint32_t)UB);
+            tma_load_3d(smem_u32(ring) + slot * UB, &tmap_w, 0, kb * T::kWordRows, cg * (kCgCols / 32), full_bar(slot));
         }
-        if (plan.push) cluster_wait();
-    } else {
-        // ===== consumer warps =====
+    };
+    // Weights are constants: the ring is filled before the dependency on the previous kernel is awaited.
+    if (warp == 0)
+        for (int u = 0; u < R && kb_begin + u < kb_end; ++u) issue_unit(kb_begin + u, u);
+
+    {
         const int g = lane >> 2, j = lane & 3;
         const int zwords = N / 32 * BITS;
         const int lane_col = warp * 32 + 4 * g;  // first of the lane's 4 columns inside the column group
         const int units_per_group = group_size / UR;
-        uint32_t* xs = reinterpret_cast<uint32_t*>(dsm + (size_t)R * UB);
+        uint32_t* xs = reinterpret_cast<uint32_t*>(ring + (size_t)R * UB);
         const int ps_pitch = max_stage_rows(M) / 8;   // ps[m * ps_pitch + octet]: (sum x, sum c*x) of 8 staged rows
-        const uint32_t lane_off = (uint32_t)(lane_col * 4);
+        // byte offsets of the lane's vecs inside a unit: line L = chunk (= warp) * word-rows + word-row, piece g ^ (L & 7)
+        uint32_t vec_off[T::kVecs];
+#pragma unroll
+        for (int r = 0; r < T::kVecs; ++r) {
+            const uint32_t L = (uint32_t)(warp * T::kWordRows + T::vec_row(j, r));
+            vec_off[r] = L * 128u + (((uint32_t)g ^ (L & 7u)) << 4);
+        }
 
         for (int m = 0; m < M; ++m) corr_sm[m][tid] = 0.f;
 
@@ -486,16 +533,8 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
                         if (BITS == 3 && zstr) hi[i] = __ldg(zp + (size_t)(gb + i) * zwords + 1);
                     }
                 }
-                if (gb == 0) {
-                    if (first_stage) {
-                        // these loads are queued; now the producer may flood the memory system with weight copies
-                        asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
-                        // x is the only operand a preceding kernel may still be writing
-                        asm volatile("griddepcontrol.wait;" ::: "memory");
-                        first_stage = false;
-                    }
-                    x_issue(tid, 0, pidx0, v0);
-                }
+                // later stages: x can be requested before the first constants are consumed (one round trip, not two)
+                if (gb == 0 && !first_stage) x_issue(tid, 0, pidx0, v0);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     if (gb + i < ng) {
@@ -507,7 +546,24 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
                     }
                 }
             }
-            TRACE(1);
+            if (first_stage) {
+                // Everything above used constants only.  x is the one operand a preceding kernel may still be
+                // writing: under programmatic dependent launch this is where the kernel waits for it, with its
+                // scales and zero-points staged and its ring full.
+                TRACE(1);
+                // One warp waits for the previous kernel; the others sleep at a hardware barrier meanwhile, so a CTA
+                // that is waiting here takes no issue slots from the CTA of the previous kernel on the same SM.
+                if (warp == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+                consumer_sync();
+                // Only now may the next kernel of the stream take SM space (it initialises, fetches its scales and
+                // zero-points and fills its ring with weights before it waits for this kernel's result).  Released
+                // any earlier, a third kernel could occupy free halves of SMs ahead of the second one; measured
+                // slower for grids that leave half of every SM free.
+                asm volatile("griddepcontrol.launch_dependents;");
+                TRACE(2);
+                first_stage = false;
+                x_issue(tid, 0, pidx0, v0);
+            }
             x_consume(tid, 0, v0);
 #pragma unroll 1
             for (int q0 = 0; q0 < rows / 4; q0 += kConsumerThreads) {
@@ -550,12 +606,15 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
 
         int kb = kb_begin, slot = 0, round = 0;
         int grp = 0;
+        CLK_DECL;
         bool pending = false;  // d holds products that have not been scaled into out yet
         while (kb < kb_end) {
             // stage as far as the stage grid and this CTA's range allow
             const int su = plan.stage_units;
             const int kb_stop = min((kb / su + 1) * su, kb_end);
+            CLK_START;
             stage(kb, kb_stop);
+            CLK_ADD(c_stage);
             grp = (kb * UR) / group_size;
             int grp_left = units_per_group - (kb - grp * units_per_group);
             const uint32_t* bsm = xs + (size_t)(g * 4 + j) * T::kBRegs;
@@ -563,15 +622,27 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
 #pragma unroll 1
             for (; kb < kb_stop; ++kb) {
                 mbar_wait(full_bar(slot), round & 1, &gave_up);
+                CLK_ADD(c_wait);
                 uint4 cur[T::kVecs];
-                const uint8_t* src = dsm + slot * UB + lane_off;
+                const uint8_t* src = ring + slot * UB;
 #pragma unroll
-                for (int r = 0; r < T::kVecs; ++r)
-                    cur[r] = *reinterpret_cast<const uint4*>(src + T::vec_row(j, r) * kRowPitch);
+                for (int r = 0; r < T::kVecs; ++r) cur[r] = *reinterpret_cast<const uint4*>(src + vec_off[r]);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(empty_bar(slot));  // the unit is in registers: the producer may refill the slot
+                // The unit is on its way to registers.  Each warp counts itself in; the last one refills the slot with
+                // the unit R further on (nobody waits for anybody).  The count is looked at after the products, so
+                // that its round trip through shared memory is not waited for.
+                unsigned int before = 0u;
+                if (lane == 0) before = atomicAdd(&taken[slot], 1u);
+                const int done_slot = slot;
                 if (++slot == R) { slot = 0; ++round; }
+                CLK_ADD(c_load);
                 T::compute(cur, bsm, g < M, d);
+                CLK_ADD(c_comp);
+                before = __shfl_sync(0xffffffffu, before, 0);
+                if (before == kConsumerWarps - 1) {
+                    if (lane == 0) taken[done_slot] = 0u;
+                    if (kb + R < kb_end) issue_unit(kb + R, done_slot);
+                }
                 bsm += bsm_step;
                 pending = true;
                 if (--grp_left == 0) {
@@ -580,10 +651,12 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
                     grp_left = units_per_group;
                     pending = false;
                 }
+                CLK_ADD(c_flush);
             }
             TRACE(5);
         }
         if (pending) flush_group(grp);
+        CLK_STORE;
 
         // ---- this CTA's partial result: combine the lanes, remove the offset / zero-point term ----
         consumer_sync();  // corr_sm is complete
@@ -655,6 +728,18 @@ gemv_stream_kernel(const __half* __restrict__ x, const int32_t* __restrict__ qwe
     TRACE(7);
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+}
+
 int ctas_per_sm() {
     static const int v = [] {
         const char* e = std::getenv("B200GPTQ_GEMV_CTAS_PER_SM");
@@ -670,8 +755,10 @@ Plan make_plan(int M, int K, int N, int group_size, int* smem_bytes) {
     constexpr int unit_rows = Traits<BITS>::kUnitRows;
     p.cgs = (N + kCgCols - 1) / kCgCols;
     p.kbs = K / unit_rows;
-    // cluster size: as many K slices as keep every CTA of the grid resident at once, at most 8.  With one
-    // CTA per SM a CTA can hold its whole slice in flight; with two, consecutive kernels can overlap.
+    // cluster size: as many K slices as keep every CTA of the grid resident at once (two per SM: a CTA takes just
+    // under half an SM's registers and shared memory), at most 8.  Measured against one CTA per SM with the next
+    // launch of the stream resident beside it: two CTAs of the same launch keep the SM's issue slots busier
+    // (16 warps instead of 8 in the unpack loop), which is worth more than hiding the next launch's start-up.
     const int per_sm = ctas_per_sm();
     const int slots = per_sm * sm_count();
     int c = slots / p.cgs;
@@ -685,26 +772,27 @@ Plan make_plan(int M, int K, int N, int group_size, int* smem_bytes) {
     if (stage_rows > cap) stage_rows = group_size <= cap ? (cap / group_size) * group_size : cap;
     p.stage_units = (int)(stage_rows / unit_rows);
     if (p.stage_units < 1) p.stage_units = 1;
-    // ring: enough unit buffers to cover the bandwidth-delay product, no more than the slice needs
+    // ring: what is left of the shared-memory budget, no more than the slice needs
     const int other = xs_bytes<BITS>(M) + s_sm_bytes() + z_sm_bytes() + corr_bytes(M) + ps_bytes(M);
-    static const int inflight_env = [] {
-        const char* e = std::getenv("B200GPTQ_GEMV_INFLIGHT_KB");
-        const int kb = e ? std::atoi(e) : 0;
-        return kb > 0 ? kb * 1024 : 0;
-    }();
-    const int inflight = inflight_env ? inflight_env : (per_sm == 1 ? 3 * kInflightBytes : kInflightBytes);
-    int ring = (inflight + unit_bytes<BITS>() - 1) / unit_bytes<BITS>();
-    const int longest = (p.kbs + c - 1) / c;
-    if (ring > longest) ring = longest;
-    if (ring > kMaxRing) ring = kMaxRing;
-    if (ring < 2) ring = 2;
-    p.ring_units = ring;
     static const bool push_env = [] {
         const char* e = std::getenv("B200GPTQ_GEMV_PUSH");
         return !(e && e[0] == '0');
     }();
     p.push = (c > 1 && push_env && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
-    *smem_bytes = ring * unit_bytes<BITS>() + other + (p.push ? red_bytes(M, c) : 0);
+    const int fixed = other + (p.push ? red_bytes(M, c) : 0);
+    static const int inflight_env = [] {
+        const char* e = std::getenv("B200GPTQ_GEMV_INFLIGHT_KB");
+        const int kb = e ? std::atoi(e) : 0;
+        return kb > 0 ? kb * 1024 : 0;
+    }();
+    const int inflight = inflight_env ? inflight_env : kSmemBudget - fixed;
+    int ring = inflight / unit_bytes<BITS>();
+    const int longest = (p.kbs + c - 1) / c;
+    if (ring > longest) ring = longest;
+    if (ring > kMaxRing) ring = kMaxRing;
+    if (ring < 2) ring = 2;
+    p.ring_units = ring;
+    *smem_bytes = ring * unit_bytes<BITS>() + fixed + 1024;   // + slack to start the ring on a 1024-byte boundary
     return p;
 }
 
@@ -732,6 +820,20 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
                                                200 * 1024));
         attr_set[dev] = true;
     }
+    // qweight [K/32*bits, N] as a 3-D tensor {32 columns, word-rows, N/32 column chunks}; a box is one unit
+    static const EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) { set_last_cuda_error((int)cudaErrorNotSupported); return B200GPTQ_ERR_CUDA; }
+    CUtensorMap tmap_w;
+    {
+        const cuuint64_t dims[3] = {32, (cuuint64_t)(K / 32 * BITS), (cuuint64_t)(N / 32)};
+        const cuuint64_t strides[2] = {(cuuint64_t)N * sizeof(int32_t), 32 * sizeof(int32_t)};
+        const cuuint32_t box[3] = {32, (cuuint32_t)Traits<BITS>::kWordRows, (cuuint32_t)(kCgCols / 32)};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(qweight), dims,
+                                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(plan.cgs * plan.cluster);
     cfg.blockDim = dim3(kThreads);
@@ -751,7 +853,7 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS>, x, qweight, qzeros, scales, x_perm, bias, y,
+    B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS>, tmap_w, x, qweight, qzeros, scales, x_perm, bias, y,
                                          M, K, N, group_size, plan, status));
     return B200GPTQ_OK;
 }
@@ -762,8 +864,11 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
 extern "C" __attribute__((visibility("default"))) int b200gptq_trace_read(unsigned long long* host, int n) {
     return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n);
 }
+extern "C" __attribute__((visibility("default"))) int b200gptq_trace_units(unsigned long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, g_trace_units, sizeof(unsigned long long) * 8 * 64);
+}
 extern "C" __attribute__((visibility("default"))) int b200gptq_trace_clear(void) {
-    trace_clear_kernel<<<8, 1024>>>();
+    trace_clear_kernel<<<80, 1024>>>();
     return (int)cudaDeviceSynchronize();
 }
 #endif
