@@ -106,9 +106,10 @@ B200GPTQ_API int b200gptq_gemv(const void* x, const int32_t* qweight, const int3
  *
  * x_perm as for b200gptq_gemv, except that a non-NULL x_perm needs
  * workspace room for the gathered copy of x (counted by b200gptq_workspace_bytes).
- * g_idx must be constant over aligned 32-row blocks (B200GPTQ_ERR_GROUPS
- * otherwise is reported through *status_word, see below); layers with an
- * arbitrary act-order g_idx are first re-ordered with b200gptq_sort_rows().
+ * g_idx must be constant over aligned 32-row blocks: the kernel takes the
+ * group of a block from the block's first row and does not check the others
+ * (that is the caller's contract); layers with an arbitrary act-order g_idx
+ * are first re-ordered with b200gptq_sort_rows().
  */
 B200GPTQ_API int b200gptq_gemm(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
                   const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
