@@ -4,6 +4,8 @@
 // step once the linears are fast (the reference leaves these to transformers' eager modules:
 // end2end/autogptq-generation-inference-benchmark.py:26-49).  All are memory-trivial; the point is
 // launch count.  fp16 storage, fp32 arithmetic.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200gptq {
@@ -22,11 +24,57 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // x[b,:] += add[b,:] (optional); h[b,:] = norm(x[b,:]) * w (+ beta).  rms != 0: RMSNorm, else LayerNorm.
 // One CTA of 256 threads per row; H is a multiple of 8.
+// Programmatic dependent launch: every kernel of the decode step is launched with the attribute that lets it
+// become resident while its predecessor in the stream is still running.  It reads and writes nothing of the
+// step's data before the predecessor has completed (griddepcontrol.wait), and only then lets its own successor
+// in (so at most two kernels of the chain are resident at a time).  Without the launch attribute both
+// instructions do nothing.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("B200GPTQ_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream, int cluster_x,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (cluster_x > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = cluster_x;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __global__ void __launch_bounds__(256)
 add_norm_kernel(__half* __restrict__ x, const __half* __restrict__ add, const __half* __restrict__ w,
                 const __half* __restrict__ beta, __half* __restrict__ h, int H, float eps, int rms) {
     extern __shared__ float row[];  // H floats
     __shared__ float red[2][8];
+    pdl_enter();
     const int b = blockIdx.x, tid = threadIdx.x;
     __half* xr = x + (size_t)b * H;
     float s = 0.f, s2 = 0.f;
@@ -83,6 +131,7 @@ __global__ void rope_cache_kernel(const __half* __restrict__ qkv, const __half* 
                                   const __half* __restrict__ sin_t, const long long* __restrict__ pos,
                                   __half* __restrict__ q_out, __half* __restrict__ k_cache,
                                   __half* __restrict__ v_cache, int heads, int hd, int max_seq, int rope) {
+    pdl_enter();
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x;  // pair index
     const int p = (int)pos[0];
     const size_t tok = (size_t)b * 3 * heads * hd;
@@ -133,6 +182,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
     __shared__ __align__(16) __half q_sm[HD];
     __shared__ float sm_m[WARPS], sm_l[WARPS], sm_acc[WARPS][HD];
     __shared__ float cta_m, cta_l, cta_acc[HD];   // this CTA's partial result, read by the cluster's first CTA
+    pdl_enter();
     const int split = blockIdx.x % kAttnSplit, head = blockIdx.x / kAttnSplit, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int L = (int)pos[0] + 1;
@@ -247,6 +297,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
 // act[b, i] = silu(u[b, i]) * u[b, I + i]  (gated != 0)   or   relu(u[b, i])  (gated == 0)
 __global__ void __launch_bounds__(256)
 act_kernel(const __half* __restrict__ u, __half* __restrict__ act, int I, int gated, size_t total) {
+    pdl_enter();
     const size_t idx = ((size_t)blockIdx.x * 256 + threadIdx.x) * 2;
     if (idx >= total) return;
     const size_t b = idx / I, i = idx % I;
@@ -276,10 +327,10 @@ B200GPTQ_API int b200gptq_add_norm(void* x, const void* add, const void* w, cons
                                    int H, float eps, int rms, void* stream) {
     if (!x || !w || !h) return B200GPTQ_ERR_NULL_POINTER;
     if (rows <= 0 || H <= 0 || H % 8 != 0 || H > 12288) return B200GPTQ_ERR_SHAPE;
-    add_norm_kernel<<<rows, 256, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__half*>(x), static_cast<const __half*>(add), static_cast<const __half*>(w),
-        static_cast<const __half*>(beta), static_cast<__half*>(h), H, eps, rms);
-    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    B200GPTQ_CUDA_TRY(launch_pdl(add_norm_kernel, dim3(rows), dim3(256), H * sizeof(float), stream, 1,
+                                 static_cast<__half*>(x), static_cast<const __half*>(add),
+                                 static_cast<const __half*>(w), static_cast<const __half*>(beta),
+                                 static_cast<__half*>(h), H, eps, rms));
     return B200GPTQ_OK;
 }
 
@@ -288,11 +339,11 @@ B200GPTQ_API int b200gptq_rope_cache(const void* qkv, const void* cos_t, const v
                                      int max_seq, int rope, void* stream) {
     if (!qkv || !pos || !q_out || !k_cache || !v_cache || (rope && (!cos_t || !sin_t))) return B200GPTQ_ERR_NULL_POINTER;
     if (batch <= 0 || heads <= 0 || hd % 2 != 0 || hd > 2048) return B200GPTQ_ERR_SHAPE;
-    rope_cache_kernel<<<dim3(heads, batch), hd / 2, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(qkv), static_cast<const __half*>(cos_t), static_cast<const __half*>(sin_t),
-        static_cast<const long long*>(pos), static_cast<__half*>(q_out), static_cast<__half*>(k_cache),
-        static_cast<__half*>(v_cache), heads, hd, max_seq, rope);
-    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    B200GPTQ_CUDA_TRY(launch_pdl(rope_cache_kernel, dim3(heads, batch), dim3(hd / 2), 0, stream, 1,
+                                 static_cast<const __half*>(qkv), static_cast<const __half*>(cos_t),
+                                 static_cast<const __half*>(sin_t), static_cast<const long long*>(pos),
+                                 static_cast<__half*>(q_out), static_cast<__half*>(k_cache),
+                                 static_cast<__half*>(v_cache), heads, hd, max_seq, rope));
     return B200GPTQ_OK;
 }
 
@@ -301,27 +352,18 @@ B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const 
                                       void* stream) {
     if (!q || !k_cache || !v_cache || !pos || !out) return B200GPTQ_ERR_NULL_POINTER;
     if (batch <= 0 || heads <= 0 || (hd != 64 && hd != 128)) return B200GPTQ_ERR_SHAPE;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(heads * kAttnSplit, batch);
-    cfg.blockDim = dim3(512);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kAttnSplit;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
     const __half* qh = static_cast<const __half*>(q);
     const __half* kh = static_cast<const __half*>(k_cache);
     const __half* vh = static_cast<const __half*>(v_cache);
     const long long* ph = static_cast<const long long*>(pos);
     __half* oh = static_cast<__half*>(out);
+    const dim3 grid(heads * kAttnSplit, batch);
     if (hd == 128) {
-        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, qh, kh, vh, ph, oh, heads, max_seq, scale));
+        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<128>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph, oh,
+                                     heads, max_seq, scale));
     } else {
-        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, qh, kh, vh, ph, oh, heads, max_seq, scale));
+        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<64>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph, oh,
+                                     heads, max_seq, scale));
     }
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
@@ -332,9 +374,8 @@ B200GPTQ_API int b200gptq_act(const void* u, void* act, int rows, int I, int gat
     if (rows <= 0 || I <= 0 || I % 2 != 0) return B200GPTQ_ERR_SHAPE;
     const size_t total = (size_t)rows * I;
     const unsigned blocks = (unsigned)((total / 2 + 255) / 256);
-    act_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(u),
-                                                                      static_cast<__half*>(act), I, gated, total);
-    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    B200GPTQ_CUDA_TRY(launch_pdl(act_kernel, dim3(blocks), dim3(256), 0, stream, 1, static_cast<const __half*>(u),
+                                 static_cast<__half*>(act), I, gated, total));
     return B200GPTQ_OK;
 }
 

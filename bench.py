@@ -211,9 +211,20 @@ def time_gemm_sweep(dev):
 def time_llama_decode(dev, world, prompt_len=512, decode_steps=256):
     """Config 3: Llama-7B architecture, 4-bit g128, batch 1, 512-token prompt, 256 greedy decode steps, TP = world."""
     from autogptq.tvm_b200 import decoder
-    cfg = decoder.LLAMA_7B
-    m = decoder.GPTQDecoder(cfg, batch=1, device=dev)
-    prompt = torch.randint(0, cfg.vocab, (1, prompt_len), generator=torch.Generator().manual_seed(11)).to(dev)
+    return time_decode(dev, world, decoder.LLAMA_7B, "llama7b_arch_int4_g128_bs1_p512_d256", 1, prompt_len, decode_steps)
+
+
+def time_opt66b_decode(dev, world):
+    """Config 4: OPT-66B architecture, 3-bit g128 act-order, batch 1 and 16, 128-token prompts, 128 decode steps."""
+    from autogptq.tvm_b200 import decoder
+    return [time_decode(dev, world, decoder.OPT_66B, f"opt66b_arch_int3_g128_act_bs{b}_p128_d128", b, 128, 128)
+            for b in (1, 16)]
+
+
+def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
+    from autogptq.tvm_b200 import decoder
+    m = decoder.GPTQDecoder(cfg, batch=batch, device=dev)
+    prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(11)).to(dev)
     m.prefill(prompt)            # warm-up (builds run-time views, sizes scratch)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -236,7 +247,7 @@ def time_llama_decode(dev, world, prompt_len=512, decode_steps=256):
     ms, prefill_ms = float(t[0]), float(t[1])
     peak, _ = measured_peaks()
     per_tok_s = ms * 1e-3 / decode_steps
-    return {"workload": "llama7b_arch_int4_g128_bs1_p512_d256", "tp": world, "decode_tok_s": decode_steps / (ms * 1e-3),
+    return {"workload": name, "tp": world, "batch": batch, "decode_tok_s": batch * decode_steps / (ms * 1e-3),
             "ms_per_token": ms / decode_steps, "prefill_ms": prefill_ms,
             "weight_bytes_per_token_per_gpu": m.bytes_per_token(),
             "frac_of_hbm_roofline": m.bytes_per_token() / per_tok_s / 1e9 / peak,
@@ -281,6 +292,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip config 0, the GEMM sweep and the decode run")
+    ap.add_argument("--opt66b", action="store_true",
+                    help="add the OPT-66B-architecture decode runs (config 4) at tensor-parallel degree --gpus")
     ap.add_argument("--gemm-demo", type=int, default=0, metavar="M",
                     help="only launch the config-2 GEMM a few times with M rows (a small target for ncu) and exit")
     args = ap.parse_args()
@@ -403,6 +416,10 @@ def main():
         torch.cuda.empty_cache()
         barrier()
         extras["llama7b_decode"] = time_llama_decode(dev, world)   # every rank takes part (tensor parallel)
+    if args.opt66b:
+        torch.cuda.empty_cache()
+        barrier()
+        extras["opt66b_decode"] = time_opt66b_decode(dev, world)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
