@@ -255,7 +255,7 @@ template <int BITS> __host__ __device__ inline int xs_bytes(int M) {
 __host__ __device__ inline int s_sm_bytes() { return kStageGroups * kCgCols * 4; }
 __host__ __device__ inline int z_sm_bytes() { return kStageGroups * kCgCols * 4; }
 __host__ __device__ inline int corr_bytes(int M) { return M * kCgCols * 4; }
-__host__ __device__ inline int ps_bytes(int M) { return M * (max_stage_rows(M) / 8) * 8; }
+__host__ __device__ inline int ps_bytes(int M) { return M * (max_stage_rows(M) / 128) * 8; }
 // landing zone of the other CTAs' partial sums (push combine): red[rank - 1][m][column]
 __host__ __device__ inline int red_bytes(int M, int cluster) { return (cluster - 1) * M * kCgCols * 4; }
 constexpr int kMaxRedBytes = 16 * 1024;   // larger combines read the partial sums remotely instead
@@ -410,7 +410,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
         const int lane_col = warp * 32 + 4 * g;  // first of the lane's 4 columns inside the column group
         const int units_per_group = group_size / UR;
         uint32_t* xs = reinterpret_cast<uint32_t*>(ring + (size_t)R * UB);
-        const int ps_pitch = max_stage_rows(M) / 8;   // ps[m * ps_pitch + octet]: (sum x, sum c*x) of 8 staged rows
+        const int ps_pitch = max_stage_rows(M) / 128;   // ps[m * ps_pitch + c]: (sum x, sum c*x) of staged rows 128c .. 128c+127
         // byte offsets of the lane's vecs inside a unit: line L = chunk (= warp) * word-rows + word-row, piece g ^ (L & 7)
         uint32_t vec_off[T::kVecs];
 #pragma unroll
@@ -502,9 +502,13 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                                 scx = fmaf(T::coef(h), xf, scx);
                             }
                         }
-                        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
-                        scx += __shfl_xor_sync(0xffffffffu, scx, 1);
-                        if (has_q && (tid & 1) == 0) ps[m * ps_pitch + (qi >> 1)] = make_float2(sx, scx);
+                        // a warp covers 128 consecutive rows, which lie in one group (group_size is a multiple of 128)
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            sx += __shfl_xor_sync(0xffffffffu, sx, o);
+                            scx += __shfl_xor_sync(0xffffffffu, scx, o);
+                        }
+                        if (has_q && lane == 0) ps[m * ps_pitch + (qi >> 5)] = make_float2(sx, scx);
                     }
                 }
             };
@@ -582,8 +586,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                 const int m = tid % M, gl = tid / M;
                 const int ra = max(r0, (g0 + gl) * group_size), rb = min(r0 + rows, (g0 + gl + 1) * group_size);
                 float sx = 0.f, scx = 0.f;
-#pragma unroll 4
-                for (int o = (ra - r0) >> 3; o < (rb - r0) >> 3; ++o) {
+                for (int o = (ra - r0) >> 7; o < (rb - r0) >> 7; ++o) {
                     const float2 p = ps[m * ps_pitch + o];
                     sx += p.x;
                     scx += p.y;
