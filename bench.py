@@ -444,7 +444,7 @@ def main():
             "e2e": {"value": world * P * wbytes / e2e_s / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": P * M * K * 2, "d2h_bytes_per_step": P * M * N * 2,
                     "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
-            "gpu_launches": args.steps * P + e2e_steps * P + sum(v.get("launches", 0) for v in extras.values()),
+            "gpu_launches": args.steps * P + e2e_steps * P + sum(v.get("launches", 0) for v in extras.values() if isinstance(v, dict)),
             "clocks": clocks,
         }
         line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
