@@ -320,11 +320,11 @@ __device__ __forceinline__ void trace_unit(int blk, int i) {
     }
 }
 #define TRACE_UNIT(i)
-#define CLK_DECL long long c_wait = 0, c_load = 0, c_comp = 0, c_flush = 0, c_stage = 0, c_t
+#define CLK_DECL long long c_wait = 0, c_load = 0, c_comp = 0, c_flush = 0, c_stage = 0, c_t, c_s0 = 0, c_s1 = 0, c_s2 = 0, c_s3 = 0, c_s4 = 0, c_s5 = 0
 #define CLK_START c_t = clock64()
 #define CLK_ADD(acc) do { const long long c_n = clock64(); acc += c_n - c_t; c_t = c_n; } while (0)
 #define CLK_STORE do { if ((threadIdx.x & 31) == 0 && blockIdx.x == 35) { unsigned long long* o = g_trace_units + (threadIdx.x >> 5) * 64; \
-    o[0] = c_wait; o[1] = c_load; o[2] = c_comp; o[3] = c_flush; o[4] = c_stage; } } while (0)
+    o[0] = c_wait; o[1] = c_load; o[2] = c_comp; o[3] = c_flush; o[4] = c_stage; o[5] = c_s0; o[6] = c_s1; o[7] = c_s2; o[8] = c_s3; o[9] = c_s4; o[10] = c_s5; } } while (0)
 #define TRACE(slot) trace_mark(slot)
 #define TRACE0(tag) trace_mark(0, tag)
 #else
@@ -338,13 +338,16 @@ __device__ __forceinline__ void trace_unit(int blk, int i) {
 #endif
 
 // One cluster per column group; CTA `rank` of the cluster owns units [rank*kbs/C, (rank+1)*kbs/C).
-template <int BITS>
+// MULTI = false is the single-row instantiation (M == 1, the decode case that is timed): every loop over the
+// rows of x and every multi-row code path folds away, which keeps the code that runs once per launch short.
+template <int BITS, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __restrict__ x,
                    const int32_t* __restrict__ qweight,
                    const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
                    const int32_t* __restrict__ x_perm, const __half* __restrict__ bias, __half* __restrict__ y,
-                   int M, int K, int N, int group_size, Plan plan, unsigned int* __restrict__ status) {
+                   int M_rows, int K, int N, int group_size, Plan plan, unsigned int* __restrict__ status) {
+    const int M = MULTI ? M_rows : 1;
     using T = Traits<BITS>;
     constexpr int UR = T::kUnitRows;
     constexpr int UB = unit_bytes<BITS>();
@@ -443,6 +446,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                 for (int r = 0; r < 4; ++r) d[cp][r] = 0.f;
         };
 
+        CLK_DECL;
         // Stage x for units [kb_a, kb_b): fragments into xs, scales and zero-points into s_sm / z_sm, and
         // the offset / zero-point term  sum_groups s * (sum c x + zero * sum x)  into corr_sm.
         auto stage = [&](int kb_a, int kb_b) {
@@ -486,30 +490,51 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                 const bool has_q = qi < rows / 4;
                 const int kl = 4 * qi;                                // row inside the stage
                 const int ul = kl / UR, r_in_unit = kl % UR;
+                int jl = 0, hh[4];
+                float cf[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    T::locate(r_in_unit + i, jl, hh[i]);   // the four rows share jl
+                    cf[i] = T::coef(hh[i]);
+                }
+                // Sums over the warp's 128 consecutive rows, which lie in one group (group_size is a multiple of
+                // 128).  With several rows of x the reductions are written level by level over all rows, so that
+                // the shuffles of different rows overlap instead of forming one long dependent chain per row.
+                float sx[4], scx[4];
+                const int nrows = min(4, M - m0);   // uniform
 #pragma unroll
                 for (int mm = 0; mm < 4; ++mm) {
-                    const int m = m0 + mm;
-                    if (m < M) {  // uniform
-                        float sx = 0.f, scx = 0.f;
-                        if (has_q) {
+                    sx[mm] = 0.f; scx[mm] = 0.f;
+                    if (mm < nrows && has_q) {
+                        const int m = m0 + mm;
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                int jl, h;
-                                T::locate(r_in_unit + i, jl, h);   // the four rows share jl
-                                xh[(size_t)(((ul * M + m) * 4 + jl) * T::kBRegs) * 2 + h] = v[mm][i];
-                                const float xf = __half2float(v[mm][i]);
-                                sx += xf;
-                                scx = fmaf(T::coef(h), xf, scx);
-                            }
+                        for (int i = 0; i < 4; ++i) {
+                            xh[(size_t)(((ul * M + m) * 4 + jl) * T::kBRegs) * 2 + hh[i]] = v[mm][i];
+                            const float xf = __half2float(v[mm][i]);
+                            sx[mm] += xf;
+                            scx[mm] = fmaf(cf[i], xf, scx[mm]);
                         }
-                        // a warp covers 128 consecutive rows, which lie in one group (group_size is a multiple of 128)
-#pragma unroll
-                        for (int o = 1; o < 32; o <<= 1) {
-                            sx += __shfl_xor_sync(0xffffffffu, sx, o);
-                            scx += __shfl_xor_sync(0xffffffffu, scx, o);
-                        }
-                        if (has_q && lane == 0) ps[m * ps_pitch + (qi >> 5)] = make_float2(sx, scx);
                     }
+                }
+                if (nrows == 1) {
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        sx[0] += __shfl_xor_sync(0xffffffffu, sx[0], o);
+                        scx[0] += __shfl_xor_sync(0xffffffffu, scx[0], o);
+                    }
+                } else {
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1)
+#pragma unroll
+                        for (int mm = 0; mm < 4; ++mm) {
+                            sx[mm] += __shfl_xor_sync(0xffffffffu, sx[mm], o);
+                            scx[mm] += __shfl_xor_sync(0xffffffffu, scx[mm], o);
+                        }
+                }
+                if (has_q && lane == 0) {
+#pragma unroll
+                    for (int mm = 0; mm < 4; ++mm)
+                        if (mm < nrows) ps[(m0 + mm) * ps_pitch + (qi >> 5)] = make_float2(sx[mm], scx[mm]);
                 }
             };
             auto perm_of = [&](int qi) {
@@ -522,6 +547,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
             // -- constants (scales, zero-points, gather indices): 8 groups of loads in flight at a time; the
             //    first pass of x loads is issued before the first constants are consumed, so that a stage
             //    costs one round trip to memory, not two
+            CLK_START;
             __half v0[4][4];
             const int4 pidx0 = perm_of(tid);
 #pragma unroll 1
@@ -550,6 +576,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                     }
                 }
             }
+            CLK_ADD(c_s0);
             if (first_stage) {
                 // Everything above used constants only.  x is the one operand a preceding kernel may still be
                 // writing: under programmatic dependent launch this is where the kernel waits for it, with its
@@ -568,7 +595,9 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                 first_stage = false;
                 x_issue(tid, 0, pidx0, v0);
             }
+            CLK_ADD(c_s1);
             x_consume(tid, 0, v0);
+            CLK_ADD(c_s2);
 #pragma unroll 1
             for (int q0 = 0; q0 < rows / 4; q0 += kConsumerThreads) {
                 const int qi = q0 + tid;
@@ -580,6 +609,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                     x_consume(qi, m0, v);
                 }
             }
+            CLK_ADD(c_s3);
             consumer_sync();
             TRACE(3);
             if (tid < ng * M) {
@@ -595,21 +625,36 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                 t_cx[gl * kMaxM + m] = scx;
             }
             consumer_sync();
-#pragma unroll 1
-            for (int m = 0; m < M; ++m) {
+            if (M == 1) {
                 float c = 0.f;
 #pragma unroll 4
                 for (int gl = 0; gl < ng; ++gl)
-                    c = fmaf(s_sm[gl][tid], fmaf(z_sm[gl][tid], t_x[gl * kMaxM + m], t_cx[gl * kMaxM + m]), c);
-                corr_sm[m][tid] += c;
+                    c = fmaf(s_sm[gl][tid], fmaf(z_sm[gl][tid], t_x[gl * kMaxM], t_cx[gl * kMaxM]), c);
+                corr_sm[0][tid] += c;
+            } else {
+                // groups outermost, rows of x innermost: eight independent sums instead of eight chains in a row
+                // (every sum still adds its groups in increasing order)
+                float c[kMaxM];
+#pragma unroll
+                for (int m = 0; m < kMaxM; ++m) c[m] = 0.f;
+#pragma unroll 2
+                for (int gl = 0; gl < ng; ++gl) {
+                    const float sg = s_sm[gl][tid], zg = z_sm[gl][tid];
+#pragma unroll
+                    for (int m = 0; m < kMaxM; ++m)
+                        if (m < M) c[m] = fmaf(sg, fmaf(zg, t_x[gl * kMaxM + m], t_cx[gl * kMaxM + m]), c[m]);
+                }
+#pragma unroll
+                for (int m = 0; m < kMaxM; ++m)
+                    if (m < M) corr_sm[m][tid] += c[m];
             }
             stage_g0 = g0;
+            CLK_ADD(c_s4);
             TRACE(4);
         };
 
         int kb = kb_begin, slot = 0, round = 0;
         int grp = 0;
-        CLK_DECL;
         bool pending = false;  // d holds products that have not been scaled into out yet
         while (kb < kb_end) {
             // stage as far as the stage grid and this CTA's range allow
@@ -819,8 +864,10 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
     int dev = 0;
     B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               200 * 1024));
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set[dev] = true;
     }
     // qweight [K/32*bits, N] as a 3-D tensor {32 columns, word-rows, N/32 column chunks}; a box is one unit
@@ -856,8 +903,13 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS>, tmap_w, x, qweight, qzeros, scales, x_perm, bias, y,
-                                         M, K, N, group_size, plan, status));
+    if (M == 1) {
+        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS, false>, tmap_w, x, qweight, qzeros, scales,
+                                             x_perm, bias, y, M, K, N, group_size, plan, status));
+    } else {
+        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS, true>, tmap_w, x, qweight, qzeros, scales,
+                                             x_perm, bias, y, M, K, N, group_size, plan, status));
+    }
     return B200GPTQ_OK;
 }
 
