@@ -340,14 +340,16 @@ __device__ __forceinline__ void trace_unit(int blk, int i) {
 // One cluster per column group; CTA `rank` of the cluster owns units [rank*kbs/C, (rank+1)*kbs/C).
 // MULTI = false is the single-row instantiation (M == 1, the decode case that is timed): every loop over the
 // rows of x and every multi-row code path folds away, which keeps the code that runs once per launch short.
-template <int BITS, bool MULTI>
+// PERM = false is the instantiation for layers whose x needs no gather (x_perm == NULL).
+template <int BITS, bool MULTI, bool PERM>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __restrict__ x,
                    const int32_t* __restrict__ qweight,
                    const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
-                   const int32_t* __restrict__ x_perm, const __half* __restrict__ bias, __half* __restrict__ y,
+                   const int32_t* __restrict__ x_perm_arg, const __half* __restrict__ bias, __half* __restrict__ y,
                    int M_rows, int K, int N, int group_size, Plan plan, unsigned int* __restrict__ status) {
     const int M = MULTI ? M_rows : 1;
+    const int32_t* __restrict__ x_perm = PERM ? x_perm_arg : nullptr;
     using T = Traits<BITS>;
     constexpr int UR = T::kUnitRows;
     constexpr int UB = unit_bytes<BITS>();
@@ -752,7 +754,9 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
     }
 
     // ---- combine the K slices of the cluster through distributed shared memory, in rank order ----
-    if (C > 1) cluster_sync_all();   // every CTA's partial result is in its corr_sm
+    // (a single row of x is always pushed when the cluster has several CTAs: the single-row kernels get here with
+    // one CTA per cluster only, and the remote part below is compiled out of them)
+    if (MULTI && C > 1) cluster_sync_all();   // every CTA's partial result is in its corr_sm
     TRACE(6);
     if (rank == 0 && warp < kConsumerWarps) {
         const int n = cg * kCgCols + tid;
@@ -762,7 +766,8 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
                 // all remote reads are issued before the first is used; the sum stays in rank order
                 float part[8];
 #pragma unroll
-                for (int r = 1; r < 8; ++r) part[r] = (r < C) ? ld_cluster_f32(&corr_sm[m][tid], (uint32_t)r) : 0.f;
+                for (int r = 1; r < 8; ++r)
+                    part[r] = (MULTI && r < C) ? ld_cluster_f32(&corr_sm[m][tid], (uint32_t)r) : 0.f;
                 float v = corr_sm[m][tid];
 #pragma unroll
                 for (int r = 1; r < 8; ++r) v += part[r];
@@ -771,7 +776,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __half* __r
             }
         }
     }
-    if (C > 1) cluster_sync_all();   // the other CTAs keep their shared memory alive until it has been read
+    if (MULTI && C > 1) cluster_sync_all();   // the other CTAs keep their shared memory alive until it has been read
     if (tid == 0 && gave_up) atomicExch(status + kStatusWord, 1u);
     TRACE(7);
 }
@@ -826,7 +831,7 @@ Plan make_plan(int M, int K, int N, int group_size, int* smem_bytes) {
         const char* e = std::getenv("B200GPTQ_GEMV_PUSH");
         return !(e && e[0] == '0');
     }();
-    p.push = (c > 1 && push_env && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
+    p.push = (c > 1 && (M == 1 || push_env) && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
     const int fixed = other + (p.push ? red_bytes(M, c) : 0);
     static const int inflight_env = [] {
         const char* e = std::getenv("B200GPTQ_GEMV_INFLIGHT_KB");
@@ -864,9 +869,13 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
     int dev = 0;
     B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, false>,
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, false, false>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, true>,
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, false, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, true, false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<BITS, true, true>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set[dev] = true;
     }
@@ -903,13 +912,10 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    if (M == 1) {
-        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS, false>, tmap_w, x, qweight, qzeros, scales,
-                                             x_perm, bias, y, M, K, N, group_size, plan, status));
-    } else {
-        B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS, true>, tmap_w, x, qweight, qzeros, scales,
-                                             x_perm, bias, y, M, K, N, group_size, plan, status));
-    }
+    auto kernel = M == 1 ? (x_perm ? gemv_stream_kernel<BITS, false, true> : gemv_stream_kernel<BITS, false, false>)
+                         : (x_perm ? gemv_stream_kernel<BITS, true, true> : gemv_stream_kernel<BITS, true, false>);
+    B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmap_w, x, qweight, qzeros, scales, x_perm, bias, y, M, K, N,
+                                         group_size, plan, status));
     return B200GPTQ_OK;
 }
 
