@@ -42,9 +42,7 @@ constexpr int kWeightGroups = 2;        // groups of such warps, taking k-tiles 
 constexpr int kMmaWarp = 1 + kWeightWarps * kWeightGroups;
 constexpr int kGemmThreads = 32 * (2 + kWeightWarps * kWeightGroups);  // TMA warp, weight warps, MMA warp
 constexpr int kPackedTileBytes = 4096;  // up to 8 word-rows x 128 columns of packed weights per k-tile
-constexpr int kMaxStages = 8;           // x tiles in flight
-constexpr int kMaxPacked = 16;          // packed-weight tiles in flight
-constexpr int kAStages = 8;             // A-operand buffers in tensor memory
+constexpr int kMaxStages = 8;
 constexpr int kTmemCols = 512;          // accumulators in columns [0, 256), A buffers in [256, 512)
 constexpr int kTmemAOffset = 256;
 constexpr int kTmemAColsPerStage = 32;  // 64 k x fp16 = 32 columns of 32 bits
@@ -220,16 +218,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
             const int32_t* __restrict__ g_idx, const __half* __restrict__ bias, __half* __restrict__ y, int M, int K,
-            int N, int group_size, int TN, int S, int P, int tab_groups, unsigned int* __restrict__ status) {
+            int N, int group_size, int TN, int S, int tab_groups, unsigned int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;            // swizzled tiles need 1024-byte alignment
     uint8_t* base_ptr = smem_raw + (base - raw);
-    // Three rings with their own depths, so that no role waits for another's slowest resource:
-    //   x tiles       (S stages of TN x 64 fp16 in shared memory)  TMA -> MMA,      freed by tcgen05.commit
-    //   packed tiles  (P stages of 4 KB in shared memory)          TMA -> producers, freed by the producers
-    //   A operands    (kAStages buffers in tensor memory)          producers -> MMA, freed by tcgen05.commit
-    __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 2 * kMaxPacked + 2 * kAStages + 1];
+    __shared__ __align__(8) uint64_t bars[3 * kMaxStages + 1];  // tma[S], a_full[S], empty[S], accum
     __shared__ uint32_t tmem_base_holder;
     __shared__ volatile int abort_flag;
 
@@ -237,33 +231,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     const int n0 = blockIdx.y * BN, m0 = blockIdx.x * TN;
     const int KT = (K + BK - 1) / BK;
     const uint32_t x_tile_bytes = (uint32_t)TN * BK * 2;
+    const uint32_t stage_bytes = x_tile_bytes + kPackedTileBytes;
 
     const uint32_t bar_base = smem_u32(bars);
-    auto x_full = [&](int s) { return bar_base + 8u * s; };                                   // x tile landed
-    auto x_empty = [&](int s) { return bar_base + 8u * (kMaxStages + s); };                   // its MMAs have retired
-    auto pk_full = [&](int s) { return bar_base + 8u * (2 * kMaxStages + s); };               // packed tile landed
-    auto pk_empty = [&](int s) { return bar_base + 8u * (2 * kMaxStages + kMaxPacked + s); };  // producers have read it
-    auto a_full = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxPacked + s); };            // A operand stored
-    auto a_empty = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxPacked + kAStages + s); }; // its MMAs have retired
-    const uint32_t accum_bar = bar_base + 8u * (2 * kMaxStages + 2 * kMaxPacked + 2 * kAStages);
-    auto x_tile = [&](int s) { return base + s * x_tile_bytes; };
-    auto p_tile = [&](int s) { return base + S * x_tile_bytes + s * kPackedTileBytes; };
+    auto tma_bar = [&](int s) { return bar_base + 8u * s; };                      // x tile + packed weights landed
+    auto full_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };      // A operand stored in tensor memory
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + s); }; // the stage's MMAs have retired
+    const uint32_t accum_bar = bar_base + 8u * (3 * kMaxStages);
+    auto x_tile = [&](int s) { return base + s * stage_bytes; };
+    auto p_tile = [&](int s) { return base + s * stage_bytes + x_tile_bytes; };
     constexpr int kWordRowsPerTile = 2 * Dequant<BITS>::kWords;     // word-rows of qweight per 64 rows of K
     constexpr uint32_t kPackedBytes = kWordRowsPerTile * BN * 4;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < S; ++s) {
-            mbar_init(x_full(s), 1);                // the TMA warp's expect_tx arrive
-            mbar_init(x_empty(s), 1);               // tcgen05.commit
-        }
-        for (int s = 0; s < P; ++s) {
-            mbar_init(pk_full(s), 1);               // the TMA warp's expect_tx arrive
-            mbar_init(pk_empty(s), kWeightWarps);   // one arrive per weight warp of the group that read it
-        }
-        for (int s = 0; s < kAStages; ++s) {
-            mbar_init(a_full(s), kWeightWarps);     // one arrive per weight warp
-            mbar_init(a_empty(s), 1);               // tcgen05.commit
+            mbar_init(tma_bar(s), 1);               // the TMA producer's expect_tx arrive
+            mbar_init(full_bar(s), kWeightWarps);   // one arrive per weight warp
+            mbar_init(empty_bar(s), 1);             // tcgen05.commit
         }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -279,36 +264,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     const uint32_t tmem_base = tmem_base_holder;
 
     if (warp == 0) {
-        // ===== TMA producer: two independent streams, each as far ahead as its ring allows =====
+        // ===== TMA producer =====
         if (lane == 0) {
-            int kp = 0, kx = 0;          // next packed tile / x tile to request
-            long long t0 = clock64();
-            while (kp < KT || kx < KT) {
-                bool progress = false;
-                if (kp < KT) {
-                    const int s = kp % P, use = kp / P;
-                    if (use == 0 || mbar_try_wait(pk_empty(s), (use - 1) & 1)) {
-                        mbar_arrive_expect_tx(pk_full(s), kPackedBytes);
-                        tma_load_2d(p_tile(s), &tmap_w, n0, kp * kWordRowsPerTile, pk_full(s));
-                        ++kp;
-                        progress = true;
-                    }
-                }
-                if (kx < KT) {
-                    const int s = kx % S, use = kx / S;
-                    if (use == 0 || mbar_try_wait(x_empty(s), (use - 1) & 1)) {
-                        mbar_arrive_expect_tx(x_full(s), x_tile_bytes);
-                        tma_load_2d(x_tile(s), &tmap_x, kx * BK, m0, x_full(s));
-                        ++kx;
-                        progress = true;
-                    }
-                }
-                if (progress) {
-                    t0 = clock64();
-                } else {
-                    if (abort_flag) break;
-                    if (clock64() - t0 > 2000000000LL) { abort_flag = 1; break; }
-                }
+            int s = 0, round = 0;
+            for (int kt = 0; kt < KT; ++kt) {
+                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, &abort_flag)) break;
+                mbar_arrive_expect_tx(tma_bar(s), x_tile_bytes + kPackedBytes);
+                tma_load_2d(p_tile(s), &tmap_w, n0, kt * kWordRowsPerTile, tma_bar(s));
+                tma_load_2d(x_tile(s), &tmap_x, kt * BK, m0, tma_bar(s));
+                if (++s == S) { s = 0; ++round; }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -316,20 +280,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
             bool ok = true;
-            int xs = 0, xround = 0;
+            int s = 0, round = 0;
             for (int kt = 0; kt < KT; ++kt) {
-                const int as = kt % kAStages;
-                ok = mbar_wait(a_full(as), (kt / kAStages) & 1, &abort_flag) && mbar_wait(x_full(xs), xround & 1, &abort_flag);
+                ok = mbar_wait(tma_bar(s), round & 1, &abort_flag) && mbar_wait(full_bar(s), round & 1, &abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t bdesc = make_smem_desc(x_tile(xs));
-                const uint32_t a_addr = tmem_base + kTmemAOffset + kTmemAColsPerStage * as;
+                const uint64_t bdesc = make_smem_desc(x_tile(s));
+                const uint32_t a_addr = tmem_base + kTmemAOffset + kTmemAColsPerStage * s;
 #pragma unroll
                 for (int k16 = 0; k16 < BK / 16; ++k16)
                     umma_f16_ts(tmem_base, a_addr + 8u * k16, bdesc + 2u * k16, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
-                umma_commit(x_empty(xs));   // frees the x stage once these MMAs have read it
-                umma_commit(a_empty(as));   // and the A buffer in tensor memory
-                if (++xs == S) { xs = 0; ++xround; }
+                umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+                if (++s == S) { s = 0; ++round; }
             }
             if (ok) umma_commit(accum_bar);
         }
@@ -351,7 +313,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         // (fp16 scale | zero-point << 16), together with the group of every 32-row block; the producers
         // then never wait on global memory inside the k loop.  Larger layers read them from global
         // memory one k-tile ahead.
-        uint32_t* tab = reinterpret_cast<uint32_t*>(base_ptr + (size_t)S * x_tile_bytes + (size_t)P * kPackedTileBytes);
+        uint32_t* tab = reinterpret_cast<uint32_t*>(base_ptr + (size_t)S * stage_bytes);
         uint16_t* gmap = reinterpret_cast<uint16_t*>(tab + (size_t)tab_groups * BN);
         auto group_of = [&](int rb) { return g_idx ? __ldg(g_idx + 32 * rb) : (32 * rb) / group_size; };
         if (tab_groups) {
@@ -388,9 +350,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         load_group(2 * wgroup + kh, g_cur, s_cur, z_cur);
 
         bool ok = true;
+        int s = wgroup % S, round = wgroup / S;
         for (int kt = wgroup; kt < KT; kt += kWeightGroups) {
             const int rb = 2 * kt + kh;
-            const int ps = kt % P, as = kt % kAStages;
             // fetch the scale / zero-point of this thread's next k-tile now, a whole iteration ahead of their use
             constexpr int kRbStep = 2 * kWeightGroups;
             if (rb + kRbStep < RB && col_ok) {
@@ -402,10 +364,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
                     else { g_nxt = g_cur; s_nxt = s_cur; z_nxt = z_cur; }
                 }
             }
-            ok = mbar_wait(pk_full(ps), (kt / P) & 1, &abort_flag);
+            // The TMA refilled this stage only after its previous MMAs retired (empty barrier), so the
+            // A buffer of the stage in tensor memory is free as well.
+            ok = mbar_wait(tma_bar(s), round & 1, &abort_flag);
             ok = __all_sync(0xffffffffu, ok);   // the tensor-memory store below is warp-collective
             if (!ok) break;
-            const uint32_t* pw = reinterpret_cast<const uint32_t*>(base_ptr + (p_tile(ps) - base)) + col;
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(base_ptr + (p_tile(s) - base)) + col;
             uint32_t cur[W];
 #pragma unroll
             for (int r = 0; r < W; ++r) cur[r] = pw[(kh * W + r) * BN];
@@ -416,21 +380,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
 #pragma unroll
                 for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(pk_empty(ps));   // the packed words are in registers
-            // the A buffer is free once the MMAs of the k-tile that used it last have retired
-            if (kt >= kAStages) {
-                ok = mbar_wait(a_empty(as), (kt / kAStages - 1) & 1, &abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            tmem_st16(lane_addr + kTmemAOffset + kTmemAColsPerStage * as + 16 * kh, out);
+            tmem_st16(lane_addr + kTmemAOffset + kTmemAColsPerStage * s + 16 * kh, out);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(a_full(as));
+            if (lane == 0) mbar_arrive(full_bar(s));
             g_cur = g_nxt; s_cur = s_nxt; z_cur = z_nxt;
+            s += kWeightGroups;
+            while (s >= S) { s -= S; ++round; }
         }
 
         // ----- epilogue: accumulators (lane = output column, column = row of x) -> fp16 -> y -----
@@ -496,17 +453,16 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) { set_last_cuda_error((int)cudaErrorNotSupported); return B200GPTQ_ERR_CUDA; }
     const int TN = pick_tn(M);
-    const int x_tile_bytes = TN * BK * 2;
-    // scale / zero-point table of the CTA's columns for every group, if it leaves room for the rings
+    const int stage_bytes = TN * BK * 2 + kPackedTileBytes;
+    // scale / zero-point table of the CTA's columns for every group, if it leaves room for >= 4 stages
     const int gs_eff = group_size;
     const int G = (K + gs_eff - 1) / gs_eff;
     int tab_bytes = G * BN * 4 + ((K / 32 * 2 + 15) / 16) * 16;
     int tab_groups = G;
-    const int P = 8;   // packed tiles in flight: 32 KB
-    if (G > 65535 || kSmemBudget - tab_bytes - P * kPackedTileBytes < 4 * x_tile_bytes) { tab_bytes = 0; tab_groups = 0; }
-    int S = (kSmemBudget - tab_bytes - P * kPackedTileBytes) / x_tile_bytes;
+    if (G > 65535 || kSmemBudget - tab_bytes < 4 * stage_bytes) { tab_bytes = 0; tab_groups = 0; }
+    int S = (kSmemBudget - tab_bytes) / stage_bytes;
     if (S > kMaxStages) S = kMaxStages;
-    const int smem_bytes = S * x_tile_bytes + P * kPackedTileBytes + tab_bytes + 1024;  // + slack to align to 1024 bytes
+    const int smem_bytes = S * stage_bytes + tab_bytes + 1024;  // + slack to align the ring to 1024 bytes
 
     CUtensorMap tmap_x, tmap_w;
     const cuuint32_t estr[2] = {1, 1};
@@ -540,7 +496,7 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
     }
     dim3 grid((M + TN - 1) / TN, (N + BN - 1) / BN);
     kernel<<<grid, kGemmThreads, smem_bytes, stream>>>(tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N,
-                                                     group_size, TN, S, P, tab_groups, status);
+                                                     group_size, TN, S, tab_groups, status);
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
 }
