@@ -1,0 +1,42 @@
+"""Host-side dispatch of QuantLinear.forward (no GPU): which entry point a given number of rows
+reaches.  The reference dispatches on M in TVMHandler.__call__ (tvm_untils/pycuda_warpper.py:138-189:
+m == 1 -> GEMV kernel, otherwise the padded GEMM buckets); here M <= 8 goes to the GEMV, more rows to
+the tensor-core GEMM for 3/4-bit layers and to GEMV passes of 8 rows for 2/8-bit layers."""
+import pytest
+import torch
+
+from autogptq.tvm_b200 import qlinear as ql
+
+
+class _FakeCuda(torch.Tensor):
+    """A CPU tensor that claims to live on a GPU, so that forward() gets as far as its dispatch."""
+    is_cuda = property(lambda self: True)
+
+
+def _layer(bits):
+    m = ql.QuantLinear(bits, 128, 256, 64, False)
+    m._ready = lambda: True
+    m._qweight_run, m._g_idx_run, m._x_perm = m.qweight, None, None
+    return m
+
+
+@pytest.mark.parametrize("bits,M,want", [
+    (4, 1, ["gemv:1"]), (4, 8, ["gemv:8"]), (4, 9, ["gemm:9"]), (3, 16, ["gemm:16"]), (4, 2048, ["gemm:2048"]),
+    (8, 8, ["gemv:8"]), (8, 20, ["gemv:8", "gemv:8", "gemv:4"]), (2, 9, ["gemv:8", "gemv:1"]),
+])
+def test_rows_decide_the_entry_point(monkeypatch, bits, M, want):
+    calls = []
+
+    def fake(name):
+        def f(x, *args, out=None, **kw):
+            calls.append(f"{name}:{x.shape[0]}")
+            return out if out is not None else torch.zeros((x.shape[0], 64), dtype=torch.float16)
+        return f
+
+    monkeypatch.setattr(ql.ops, "gemv", fake("gemv"))
+    monkeypatch.setattr(ql.ops, "gemm", fake("gemm"))
+    monkeypatch.setattr(torch, "empty", lambda *a, device=None, **k: torch.zeros(*a, **k))
+    x = torch.zeros((M, 256), dtype=torch.float16).as_subclass(_FakeCuda)
+    y = _layer(bits).forward(x)
+    assert calls == want
+    assert tuple(y.shape) == (M, 64)
