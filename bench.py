@@ -69,23 +69,29 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index),
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
+        # nvidia-smi needs a moment before its first line: wait for it, so that samples exist once the load starts
+        t_end = time.perf_counter() + 2.0
+        while not self.samples and time.perf_counter() < t_end:
+            time.sleep(0.01)
 
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6:
-                self.samples.append(parts)
+                self.samples.append((time.perf_counter(), parts))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Median SM clock and throttle reasons of the samples taken between ``t_begin`` and ``t_end``
+        (host clock around the GPU load; all samples if not given)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -93,7 +99,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        picked = [p for t, p in self.samples
+                  if (t_begin is None or t >= t_begin) and (t_end is None or t <= t_end + 0.03)]
+        for s in picked:
             try:
                 sm.append(float(s[0]))
                 mx.append(float(s[1]))
@@ -363,12 +371,13 @@ def main():
         if world > 1:
             dist.barrier()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t_load = time.perf_counter()      # the GPU runs the same load from here (warm-up) to the end of the timed steps
     for _ in range(args.warmup):
         graph.replay()
     torch.cuda.synchronize()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
@@ -377,7 +386,7 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
+    clocks = sampler.stop(t_load, time.perf_counter())
     barrier()
 
     # ---- end to end through QuantLinear.forward with host buffers ----
