@@ -25,6 +25,7 @@ int sm_count() {
 // implemented in the kernel translation units
 int dequant_dispatch(const int32_t*, const int32_t*, const __half*, const int32_t*, int, int, int, int, int8_t*,
                      __half*, cudaStream_t);
+int pack_fields_dispatch(const int32_t*, int, int, int, int32_t*, cudaStream_t);
 int sort_rows_dispatch(const int32_t*, const int32_t*, const int32_t*, int, int, int, int32_t*, int32_t*,
                        cudaStream_t);
 int gemv_generic_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*,
@@ -86,6 +87,13 @@ int b200gptq_dequant(const int32_t* qweight, const int32_t* qzeros, const void* 
     if (!q_out && !w_out) return B200GPTQ_OK;
     return dequant_dispatch(qweight, qzeros, static_cast<const __half*>(scales), g_idx, K, N, bits, group_size,
                             q_out, static_cast<__half*>(w_out), static_cast<cudaStream_t>(stream));
+}
+
+int b200gptq_pack_fields(const int32_t* vals, int R, int C, int bits, int32_t* out, void* stream) {
+    if (!vals || !out) return B200GPTQ_ERR_NULL_POINTER;
+    if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return B200GPTQ_ERR_BITS;
+    if (R <= 0 || C <= 0 || R % 32 != 0) return B200GPTQ_ERR_SHAPE;
+    return pack_fields_dispatch(vals, R, C, bits, out, static_cast<cudaStream_t>(stream));
 }
 
 int b200gptq_sort_rows(const int32_t* qweight, const int32_t* g_idx, const int32_t* perm, int K, int N, int bits,

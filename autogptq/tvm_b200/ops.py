@@ -71,6 +71,20 @@ def dequantize(qweight, qzeros, scales, g_idx, bits: int, group_size: int,
     return q, w
 
 
+def pack_fields(vals, bits: int):
+    """Pack ``vals`` (int32 CUDA tensor ``[R, C]``, ``R % 32 == 0``) along dim 0 into GPTQ int32 words
+    ``[R/32*bits, C]``; values wider than ``bits`` spill into neighbouring fields like the reference's pack."""
+    _need_cuda("vals", vals, torch.int32)
+    if vals.dim() != 2 or vals.shape[0] % 32 != 0:
+        raise ValueError(f"vals must be [R, C] with R % 32 == 0, got {tuple(vals.shape)}")
+    R, C = vals.shape
+    out = torch.empty((R // 32 * bits, C), dtype=torch.int32, device=vals.device)
+    with torch.cuda.device(vals.device):
+        st = _lib.lib.b200gptq_pack_fields(_ptr(vals), R, C, bits, _ptr(out), _stream(vals.device))
+    _lib.check(st, "b200gptq_pack_fields")
+    return out
+
+
 def sort_rows(qweight, g_idx, bits: int):
     """Re-order the rows of an act-order layer by group.  Returns
     ``(qweight_sorted, perm, g_idx_sorted)``; ``perm`` is the stable argsort of ``g_idx``."""

@@ -85,7 +85,9 @@ class QuantLinear(nn.Module):
     def pack(self, linear, scales, zeros, g_idx=None):
         """Same contract as ``QuantLinear.pack`` of the reference (qlinear.py:77-175):
         ``scales`` / ``zeros`` are ``[outfeatures, G]``; the integer weight is
-        ``round((W + zero*scale) / fp16(scale))`` per row group and ``zeros - 1`` is stored."""
+        ``round((W + zero*scale) / fp16(scale))`` per row group and ``zeros - 1`` is stored.
+        With the layer and the statistics on a CUDA device the whole procedure runs there (the
+        reference packs with a Python loop over the rows on the CPU); the result is bit-identical."""
         W = linear.weight.data.clone()
         if isinstance(linear, nn.Conv2d):
             W = W.flatten(1)
@@ -100,6 +102,13 @@ class QuantLinear(nn.Module):
         if linear.bias is not None:
             self.bias = linear.bias.detach().clone().half()
         intweight = torch.round((W.t() + scale_zeros[g]) / self.scales[g]).to(torch.int)
+        if W.is_cuda:
+            # everything on the GPU: the same element-wise arithmetic, words built by b200gptq_pack_fields
+            self.qweight = ops.pack_fields(intweight.contiguous(), self.bits)
+            zq = (zeros - 1).to(torch.int64).to(torch.int32)
+            self.qzeros = ops.pack_fields(zq.t().contiguous(), self.bits).t().contiguous()
+            self._ready_for = None
+            return
         intweight = torch.from_numpy(intweight.numpy().astype(np.uint32).astype(np.int64))
         self.qweight = _pack_fields(intweight, self.bits)
         zq = torch.from_numpy((zeros - 1).numpy().astype(np.uint32).astype(np.int64))

@@ -117,6 +117,16 @@ B200GPTQ_API int b200gptq_gemm(const void* x, const int32_t* qweight, const int3
                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Pack integer fields into GPTQ words: vals int32 [R, C] (R % 32 == 0, one field per element, packed
+ * along R) -> out int32 [R/32*bits, C], bits in {2,3,4,8}.  This is the word-building half of
+ * QuantLinear.pack of the reference (auto_gptq/nn_modules/qlinear.py:111-134 for qweight, called on
+ * [K, N]; :140-170 for qzeros, called on the transposed [N, G] zero-points), a Python loop over the
+ * rows there.  Like that loop it does not mask: a value wider than `bits` spills into the
+ * neighbouring fields.
+ */
+B200GPTQ_API int b200gptq_pack_fields(const int32_t* vals, int R, int C, int bits, int32_t* out, void* stream);
+
+/*
  * Re-order the rows of a packed layer so that rows of one group are adjacent
  * (stable sort of k by g_idx[k]).  Outputs:
  *   qweight_sorted int32 [K/32*bits, N]   row r holds original row perm[r]
