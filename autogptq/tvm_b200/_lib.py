@@ -24,6 +24,7 @@ _SIGNATURES = {
     "b200gptq_dequant": (_c_int, [_c_void_p] * 4 + [_c_int] * 4 + [_c_void_p] * 3),
     "b200gptq_workspace_bytes": (_c_size_t, [_c_int] * 5),
     "b200gptq_gemv": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
+    "b200gptq_gemv_path": (_c_int, [_c_int] * 6),
     "b200gptq_gemm": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_sort_rows": (_c_int, [_c_void_p] * 3 + [_c_int] * 3 + [_c_void_p] * 3),
     "b200gptq_pack_fields": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]),
@@ -75,6 +76,15 @@ def check(status: int, where: str) -> None:
         if status in (-2, -3, -4):
             raise ValueError(str(B200GPTQError(status, where)))
         raise B200GPTQError(status, where)
+
+
+PATH_STREAM = 1
+PATH_GENERIC = 2
+
+
+def gemv_path(M: int, K: int, N: int, bits: int, group_size: int, has_g_idx: bool) -> int:
+    """Which kernel ``b200gptq_gemv`` runs: ``PATH_STREAM`` or ``PATH_GENERIC``."""
+    return int(lib.b200gptq_gemv_path(M, K, N, bits, group_size, 1 if has_g_idx else 0))
 
 
 def workspace_bytes(op: int, M: int, K: int, N: int, bits: int) -> int:

@@ -117,6 +117,13 @@ size_t b200gptq_workspace_bytes(int op, int M, int K, int N, int bits) {
     return 0;
 }
 
+int b200gptq_gemv_path(int M, int K, int N, int bits, int group_size, int has_g_idx) {
+    if (int st = check_layer(K, N, bits, &group_size)) return st;
+    if (M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
+    return (!has_g_idx && gemv_stream_supported(M, K, N, bits, group_size)) ? B200GPTQ_PATH_STREAM
+                                                                           : B200GPTQ_PATH_GENERIC;
+}
+
 int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
                   const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
                   int bits, int group_size, void* workspace, size_t workspace_bytes, void* stream) {

@@ -90,13 +90,30 @@ B200GPTQ_API size_t b200gptq_workspace_bytes(int op, int M, int K, int N, int bi
  *           x[m, x_perm[r]] instead of x[m, r]: this is how a layer whose rows
  *           were re-ordered by b200gptq_sort_rows() is evaluated.
  *
- * Any g_idx is accepted.  Rows whose aligned 32-row block shares one group take
- * the streaming path; other blocks take a slower per-row path.
+ * Any g_idx is accepted, but g_idx == NULL is the fast-path contract: only then
+ * (and with bits in {3,4}, K and group_size multiples of 128) does the call run
+ * the streaming tensor-map kernel; every non-NULL g_idx, even one equal to
+ * k / group_size, runs the general kernel, which looks groups up per row block.
+ * Callers that hold a checkpoint's g_idx should compare it with k / group_size
+ * once at load time and pass NULL when it matches (act-order layers: re-order
+ * with b200gptq_sort_rows() first, which usually yields k / group_size again).
+ * b200gptq_gemv_path() tells which kernel a call will run.
  */
 B200GPTQ_API int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
                   const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
                   int M, int K, int N, int bits, int group_size,
                   void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Which kernel b200gptq_gemv runs for this problem: B200GPTQ_PATH_STREAM or
+ * B200GPTQ_PATH_GENERIC (a negative B200GPTQ_ERR_* code for an invalid problem).
+ * Host-only; launches nothing.  has_g_idx != 0 means a non-NULL g_idx is passed.
+ * The reference picks its kernel per (bits, N, K, M bucket) in
+ * pycuda_warpper.py:138-189; this is the query for the same decision here.
+ */
+#define B200GPTQ_PATH_STREAM 1
+#define B200GPTQ_PATH_GENERIC 2
+B200GPTQ_API int b200gptq_gemv_path(int M, int K, int N, int bits, int group_size, int has_g_idx);
 
 /*
  * Prefill GEMM, any M >= 1 (meant for M >= 16):  y = x @ W (+ bias) on the

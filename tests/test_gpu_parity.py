@@ -114,19 +114,63 @@ GEMV_CASES = [
 ]
 
 
+def _trivial_g_idx(layer):
+    gs = layer.group_size if layer.group_size != -1 else layer.K
+    return bool(torch.equal(layer.g_idx.long(), torch.arange(layer.K) // gs))
+
+
 @pytest.mark.parametrize("bits,K,N,gs,act,bias", GEMV_CASES)
 @pytest.mark.parametrize("M", [1, 2, 5, 8])
-def test_gemv_vs_oracle(bits, K, N, gs, act, bias, M):
+@pytest.mark.parametrize("explicit_g_idx", [False, True])
+def test_gemv_vs_oracle(bits, K, N, gs, act, bias, M, explicit_g_idx):
+    """``explicit_g_idx=False`` passes NULL for layers whose g_idx is k // group_size, which is the contract
+    of the streaming kernel; ``True`` always passes the tensor, which selects the general kernel.  Each
+    case asserts which kernel it ran."""
     if M not in (1, 8) and K * N > 4096 * 4096:
         pytest.skip("large shapes are covered at M = 1 and 8")
     layer = synth.make_layer(bits, K, N, gs, act, bias=bias, seed=K + N + bits)
+    if not explicit_g_idx and not _trivial_g_idx(layer):
+        pytest.skip("an act-order g_idx cannot be passed as NULL (the sorted-rows test covers that route)")
     x = synth.make_x(M, K, seed=M)
     _, _, W = O.dequantize(*_layer_np(layer), bits)
     d = layer.to(DEV)
-    y = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, d.g_idx, bits, gs, bias=d.bias)
+    g = d.g_idx if explicit_g_idx else None
+    path = _lib.gemv_path(M, K, N, bits, gs, g is not None)
+    streams = (not explicit_g_idx) and bits in (3, 4) and K % 128 == 0 and (gs == -1 or gs % 128 == 0)
+    assert path == (_lib.PATH_STREAM if streams else _lib.PATH_GENERIC)
+    y = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, g, bits, gs, bias=d.bias)
     _check_output(y, x.numpy(), W, None if layer.bias is None else layer.bias.numpy())
-    y2 = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, d.g_idx, bits, gs, bias=d.bias)
+    y2 = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, g, bits, gs, bias=d.bias)
     assert torch.equal(y, y2), "two runs on the same inputs must agree bit for bit"
+
+
+STREAM_CASES = [
+    # bits, K, N, gs, bias : shapes that stress the streaming kernel's work split
+    (4, 4096, 4096, 128, True),          # config 0 with bias through the pushed combine
+    (3, 4096, 11008, 128, False),        # config-1 shape without act-order: uneven K split (32 units over 6 CTAs)
+    (4, 11008, 4096, 128, False),        # 86 units per column group
+    (3, 11008, 4096, 128, True),
+    (4, 1024, 1056, 128, True),          # N not a multiple of 256 with clusters > 1
+    (3, 2048, 2080, 256, False),         # group of two units, ragged last column group
+    (4, 8192, 512, 1024, False),         # few column groups, long slices, groups of 8 units
+    (3, 36864, 1024, 128, False),        # slices longer than the ring and than one stage of x
+    (4, 1536, 256, -1, False),           # one group over all rows
+    (3, 128, 32, 128, False),            # one unit, one column chunk
+]
+
+
+@pytest.mark.parametrize("bits,K,N,gs,bias", STREAM_CASES)
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_streaming_gemv_vs_oracle(bits, K, N, gs, bias, M):
+    layer = synth.make_layer(bits, K, N, gs, False, bias=bias, seed=3 * K + N + bits)
+    x = synth.make_x(M, K, seed=10 + M)
+    _, _, W = O.dequantize(*_layer_np(layer), bits)
+    d = layer.to(DEV)
+    assert _lib.gemv_path(M, K, N, bits, gs, False) == _lib.PATH_STREAM
+    y = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias)
+    _check_output(y, x.numpy(), W, None if layer.bias is None else layer.bias.numpy())
+    y2 = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias)
+    assert torch.equal(y, y2)
 
 
 @pytest.mark.parametrize("bits,K,N,gs", [(4, 4096, 4096, 128), (3, 4096, 11008, 128), (4, 1024, 544, 64)])
