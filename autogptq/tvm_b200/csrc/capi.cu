@@ -9,16 +9,16 @@ static thread_local int tls_last_cuda_error = 0;
 void set_last_cuda_error(int err) { tls_last_cuda_error = err; }
 
 int sm_count() {
-    static std::mutex mu;
-    static int cached[64] = {0};
+    // looked up once per device; afterwards the launch path only reads (no lock)
+    static std::once_flag once[64];
+    static int cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    std::lock_guard<std::mutex> lock(mu);
-    if (cached[dev] == 0) {
+    std::call_once(once[dev], [dev] {
         int n = 0;
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
         cached[dev] = n;
-    }
+    });
     return cached[dev];
 }
 
@@ -152,6 +152,8 @@ int b200gptq_gemm(const void* x, const int32_t* qweight, const int32_t* qzeros, 
     if (int st = check_layer(K, N, bits, &group_size)) return st;
     if (bits != 3 && bits != 4) return B200GPTQ_ERR_BITS;
     if (M < 1) return B200GPTQ_ERR_SHAPE;
+    // the kernel takes one group per aligned 32-row block: without a g_idx that holds only for such group sizes
+    if (!g_idx && group_size % 32 != 0) return B200GPTQ_ERR_GROUPS;
     if (!aligned16(qweight) || !aligned16(x) || !aligned16(y) || !aligned16(scales) || !aligned16(qzeros))
         return B200GPTQ_ERR_ALIGNMENT;
     const size_t need = b200gptq_workspace_bytes(B200GPTQ_OP_GEMM, M, K, N, bits);

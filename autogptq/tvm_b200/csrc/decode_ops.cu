@@ -133,7 +133,11 @@ __global__ void rope_cache_kernel(const __half* __restrict__ qkv, const __half* 
                                   __half* __restrict__ v_cache, int heads, int hd, int max_seq, int rope) {
     pdl_enter();
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x;  // pair index
-    const int p = (int)pos[0];
+    const long long p64 = pos[0];
+    // The position lives in device memory (a captured graph advances it), so the host cannot check it per launch:
+    // a position outside the caches is refused here, with no access issued.
+    if (p64 < 0 || p64 >= max_seq) return;
+    const int p = (int)p64;
     const size_t tok = (size_t)b * 3 * heads * hd;
     const __half2 q2 = *reinterpret_cast<const __half2*>(qkv + tok + (size_t)head * hd + 2 * i);
     const __half2 k2 = *reinterpret_cast<const __half2*>(qkv + tok + (size_t)(heads + head) * hd + 2 * i);
@@ -185,7 +189,8 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
     pdl_enter();
     const int split = blockIdx.x % kAttnSplit, head = blockIdx.x / kAttnSplit, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int L = (int)pos[0] + 1;
+    const long long p64 = pos[0];
+    const int L = p64 < 0 ? 0 : (p64 >= max_seq ? max_seq : (int)p64 + 1);   // never past the end of the caches
     const size_t base = ((size_t)b * heads + head) * (size_t)max_seq * HD;
     if (threadIdx.x < HD) q_sm[threadIdx.x] = q[((size_t)b * heads + head) * HD + threadIdx.x];
     __syncthreads();

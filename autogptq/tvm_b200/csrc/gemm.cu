@@ -28,6 +28,8 @@
 // Replaces the TVM-generated wmma kernels src/kernels/gemm_kernel.cu:25-142 of the reference.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200gptq {
@@ -485,15 +487,17 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
     }
 
-    static bool attr_set[64][2] = {};
+    // the shared-memory opt-in is set once per device and bit width; afterwards the launch path only reads
+    static std::once_flag attr_once[64];
+    static int attr_result[64];
     int dev = 0;
     B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B200GPTQ_ERR_TOO_LARGE;
     auto kernel = gemm_kernel<BITS>;
-    if (dev >= 0 && dev < 64 && !attr_set[dev][BITS == 4]) {
-        B200GPTQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               226 * 1024));
-        attr_set[dev][BITS == 4] = true;
-    }
+    std::call_once(attr_once[dev], [dev, kernel] {
+        attr_result[dev] = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    });
+    if (attr_result[dev] != 0) { set_last_cuda_error(attr_result[dev]); return B200GPTQ_ERR_CUDA; }
     dim3 grid((M + TN - 1) / TN, (N + BN - 1) / BN);
     kernel<<<grid, kGemmThreads, smem_bytes, stream>>>(tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N,
                                                      group_size, TN, S, tab_groups, status);

@@ -15,8 +15,8 @@
 //    array keeps whatever the previous call left: the kernels return their arrival counters to
 //    zero before they finish and write every partial-sum slot before reading it, so nothing else
 //    needs clearing between calls;
-//  * the first call on each device resolves the array's device address and zero-fills the counter
-//    region with synchronous runtime calls.  Make that first call outside any stream capture.
+//  * the first call on each device resolves the array's device address with a runtime call
+//    (cudaGetSymbolAddress).  Make that first call outside any stream capture.
 #include <mutex>
 
 #include "common.cuh"
@@ -49,8 +49,9 @@ int static_scratch(void** out) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     if (!g_scratch_ptr[dev]) {
         void* ptr = nullptr;
+        // The array is zero-initialised static storage and the kernels leave their counters at zero, so nothing has
+        // to be cleared here (a memset on the default stream would not be ordered with the caller's stream anyway).
         B200GPTQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
-        B200GPTQ_CUDA_TRY(cudaMemset(ptr, 0, kCounterBytes));  // arrival counters start at zero
         g_scratch_ptr[dev] = ptr;
     }
     *out = g_scratch_ptr[dev];

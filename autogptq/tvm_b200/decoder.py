@@ -13,9 +13,10 @@ be captured in a CUDA graph and the linears can be sharded:
 * the vocabulary projection stays dense fp16 (``modeling/_base.py:534`` keeps lm_head out of the
   quantised set) and is sharded over the vocabulary; ranks exchange their best (logit, token).
 
-Weights are random (no checkpoints offline): every rank draws its own shards directly with the
-shapes and value distributions of the benchmark configuration, so the full model is never
-materialised on one device.
+Weights are random (no checkpoints offline) but the model is ONE model at every tensor-parallel degree:
+every rank draws each full layer from a seed that does not depend on the rank, cuts its shard out of it
+with the rules of :mod:`tp` and drops the rest, so a run on N GPUs computes the same function as a run on
+one (up to the summation order of the row-parallel layers).
 """
 from __future__ import annotations
 
@@ -27,7 +28,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import ops, synth
+from . import ops, synth, tp
 from .qlinear import QuantLinear
 
 
@@ -59,26 +60,30 @@ OPT_66B = DecoderConfig(arch="opt", layers=64, hidden=9216, heads=72, inter=3686
                         group_size=128, desc_act=True, max_seq=256)
 
 
-def split_even(total: int, parts: int, unit: int) -> List[int]:
-    """Split ``total`` (a multiple of ``unit``) into ``parts`` multiples of ``unit``, as evenly as possible."""
-    n = total // unit
-    base, extra = divmod(n, parts)
-    return [(base + (1 if r < extra else 0)) * unit for r in range(parts)]
+def check_positions(pos: int, steps: int, max_seq: int) -> None:
+    """Refuse a run that would step past the KV caches: the kernels take the position from device memory (so that a
+    captured graph can advance it), which leaves this host-side check as the place where a bad request is reported."""
+    if pos < 0 or steps < 0 or pos + steps > max_seq:
+        raise ValueError(f"{steps} steps from position {pos} do not fit the KV caches (max_seq = {max_seq})")
 
 
-def _make_qlinear(cfg: DecoderConfig, K: int, N: int, bias: bool, seed: int, device) -> QuantLinear:
-    layer = synth.make_layer(cfg.bits, K, N, cfg.group_size, cfg.desc_act, bias=bias, seed=seed, device=device,
-                             scale_mult=cfg.scale_mult)
-    m = QuantLinear(cfg.bits, cfg.group_size, K, N, bias)
+def _full_layer(cfg: DecoderConfig, K: int, N: int, bias: bool, seed: int, device) -> synth.PackedLayer:
+    return synth.make_layer(cfg.bits, K, N, cfg.group_size, cfg.desc_act, bias=bias, seed=seed, device=device,
+                            scale_mult=cfg.scale_mult)
+
+
+def _to_module(layer: synth.PackedLayer, device) -> QuantLinear:
+    """A QuantLinear that owns the tensors of ``layer`` (a full layer or a shard), ready to run."""
+    m = QuantLinear(layer.bits, layer.group_size, layer.K, layer.N, layer.bias is not None)
     m.qweight, m.qzeros, m.scales, m.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
-    if bias:
+    if layer.bias is not None:
         m.bias = layer.bias
     m = m.to(device)
     m.post_init()
-    if m._x_perm is not None:
-        m.qweight = m._qweight_run      # keep only the re-ordered copy of the weights
-        m.g_idx = m._g_idx_run if m._g_idx_run is not None else \
-            (torch.arange(K, device=device) // cfg.group_size).to(torch.int32)
+    if m._x_perm is not None and m._g_idx_run is None:
+        # rows re-ordered by group and back to k // group_size: keep only the re-ordered copy of the weights
+        m.qweight = m._qweight_run
+        m.g_idx = (torch.arange(layer.K, device=device) // m.groupsize).to(torch.int32)
         m._ready_for = (m.qweight.device, m.qweight.data_ptr(), m.g_idx.data_ptr())
     return m
 
@@ -87,17 +92,21 @@ class DecoderLayer:
     def __init__(self, cfg: DecoderConfig, idx: int, rank: int, world: int, device):
         self.cfg = cfg
         hd = cfg.head_dim
-        heads_local = split_even(cfg.heads, world, 1)[rank]
-        inter_local = split_even(cfg.inter, world, cfg.group_size)[rank]
-        self.heads_local, self.inter_local = heads_local, inter_local
-        attn_local = heads_local * hd
+        head_sizes = [h * hd for h in tp.split_sizes(cfg.heads, world, 1)]       # columns of q (= k = v) per rank
+        inter_sizes = tp.split_sizes(cfg.inter, world, cfg.group_size)          # FFN width per rank, whole groups
+        self.heads_local, self.inter_local = head_sizes[rank] // hd, inter_sizes[rank]
         bias = cfg.arch == "opt"
-        seed = 100000 * rank + 10 * idx
-        self.qkv = _make_qlinear(cfg, cfg.hidden, 3 * attn_local, bias, seed + 1, device)
-        self.o = _make_qlinear(cfg, attn_local, cfg.hidden, bias and rank == 0, seed + 2, device)
-        n_up = (2 if cfg.arch == "llama" else 1) * inter_local
-        self.up = _make_qlinear(cfg, cfg.hidden, n_up, bias, seed + 3, device)
-        self.down = _make_qlinear(cfg, inter_local, cfg.hidden, bias and rank == 0, seed + 4, device)
+        up_parts = 2 if cfg.arch == "llama" else 1
+        seed = 10 * idx          # the same on every rank: the full layer is drawn, the shard cut out, the rest dropped
+        full = _full_layer(cfg, cfg.hidden, 3 * cfg.hidden, bias, seed + 1, device)
+        self.qkv = _to_module(tp.shard_column(full, rank, world, parts=3, sizes=head_sizes), device)
+        full = _full_layer(cfg, cfg.hidden, cfg.hidden, bias, seed + 2, device)
+        self.o = _to_module(tp.shard_row(full, rank, world, sizes=head_sizes)[0], device)
+        full = _full_layer(cfg, cfg.hidden, up_parts * cfg.inter, bias, seed + 3, device)
+        self.up = _to_module(tp.shard_column(full, rank, world, parts=up_parts, sizes=inter_sizes), device)
+        full = _full_layer(cfg, cfg.inter, cfg.hidden, bias, seed + 4, device)
+        self.down = _to_module(tp.shard_row(full, rank, world, sizes=inter_sizes)[0], device)
+        del full
         g = torch.Generator(device=device).manual_seed(seed + 5)
         self.norm1_w = 1.0 + 0.01 * torch.randn(cfg.hidden, generator=g, device=device, dtype=torch.float16)
         self.norm2_w = 1.0 + 0.01 * torch.randn(cfg.hidden, generator=g, device=device, dtype=torch.float16)
@@ -123,13 +132,17 @@ def _rmsnorm(x, w, eps=1e-6):
 class GPTQDecoder:
     """Batch of sequences, one token per step after the prompt; greedy sampling."""
 
-    def __init__(self, cfg: DecoderConfig, batch: int = 1, device="cuda", group=None, fused: bool = True):
+    def __init__(self, cfg: DecoderConfig, batch: int = 1, device="cuda", group=None, fused: bool = True,
+                 single: bool = False, fused_allreduce: bool = False):
+        """``single=True`` builds the whole model on this device even inside a process group (the unsharded
+        yardstick of a tensor-parallel run)."""
         self.cfg, self.batch = cfg, batch
         self.fused = fused and cfg.head_dim in (64, 128)   # decode steps use the fused helper kernels
         self.device = torch.device(device)
         self.group = group
-        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized() and not single) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.last_logits: Optional[torch.Tensor] = None   # this rank's slice of the latest logits [B, vocab_local]
         dev = self.device
         self.layers = [DecoderLayer(cfg, i, self.rank, self.world, dev) for i in range(cfg.layers)]
         g = torch.Generator(device=dev).manual_seed(7)   # replicated tensors: the same seed on every rank
@@ -141,8 +154,16 @@ class GPTQDecoder:
         self.final_norm_b = torch.zeros(cfg.hidden, device=dev, dtype=torch.float16) if cfg.arch == "opt" else None
         vocab_pad = (cfg.vocab + self.world * 8 - 1) // (self.world * 8) * (self.world * 8)
         self.vocab_local = vocab_pad // self.world
-        gl = torch.Generator(device=dev).manual_seed(9000 + self.rank)
-        self.lm_head = (0.02 * torch.randn(cfg.hidden, self.vocab_local, generator=gl, device=dev)).half()
+        # The vocabulary projection is drawn row by row of its transpose, so that a rank's slice holds the same
+        # numbers whatever the padding (which depends on the number of ranks).
+        gl = torch.Generator(device=dev).manual_seed(9000)
+        head_t = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gl, device=dev)).half()
+        lo = self.rank * self.vocab_local
+        sl = head_t[lo:lo + self.vocab_local]
+        if sl.shape[0] < self.vocab_local:   # the last rank's padding columns
+            sl = torch.cat([sl, torch.zeros(self.vocab_local - sl.shape[0], cfg.hidden, device=dev, dtype=torch.float16)])
+        self.lm_head = sl.t().contiguous()
+        del head_t
         hd = cfg.head_dim
         for L in self.layers:
             L.k_cache = torch.zeros(batch, L.heads_local, cfg.max_seq, hd, device=dev, dtype=torch.float16)
@@ -155,6 +176,7 @@ class GPTQDecoder:
         self.tokens = torch.zeros(batch, dtype=torch.long, device=dev)
         self.positions = torch.arange(cfg.max_seq, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._pos_host = 0   # host copy of the position, for range checks
 
     # ---- pieces ----
     def _norm(self, x, w, b):
@@ -210,10 +232,16 @@ class GPTQDecoder:
 
     def _sample(self, x_last):
         h = self._norm(x_last, self.final_norm_w, self.final_norm_b)
+        self.last_hidden = h
         return self._pick(h @ self.lm_head)                                    # [B, vocab_local]
 
     def _pick(self, logits):
-        val, idx = logits.float().max(dim=-1)
+        logits = logits.float()
+        pad = (self.rank + 1) * self.vocab_local - self.cfg.vocab   # padding columns of the last rank's slice
+        if pad > 0:
+            logits[:, self.vocab_local - pad:] = float("-inf")
+        self.last_logits = logits
+        val, idx = logits.max(dim=-1)
         idx = idx + self.rank * self.vocab_local
         if self.world > 1:
             vals = [torch.empty_like(val) for _ in range(self.world)]
@@ -229,6 +257,8 @@ class GPTQDecoder:
     def prefill(self, prompt: torch.Tensor):
         """prompt: int64 [B, S]; fills the KV cache and leaves the first generated token in self.tokens."""
         B, S = prompt.shape
+        check_positions(0, S, self.cfg.max_seq)
+        self._pos_host = S
         pos_idx = torch.arange(S, device=self.device)
         x = self._embed(prompt, pos_idx)
         for L in self.layers:
@@ -268,12 +298,14 @@ class GPTQDecoder:
             ops.act(u, a, L.inter_local, rms)
             delta = self._all_reduce(L.down(a))
         ops.add_norm(x, delta, self.final_norm_w, self.final_norm_b, h, eps, rms)
+        self.last_hidden = h
         logits = h @ self.lm_head
         self.tokens.copy_(self._pick(logits))
         self.pos.add_(1)
 
     def capture(self):
         """Warm up (allocates scratch, builds run-time views) and capture one decode step in a CUDA graph."""
+        check_positions(self._pos_host, 3, self.cfg.max_seq)   # two warm-up steps and the captured one
         saved_pos, saved_tok = self.pos.clone(), self.tokens.clone()
         s = torch.cuda.Stream(self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
@@ -289,6 +321,8 @@ class GPTQDecoder:
         self.tokens.copy_(saved_tok)
 
     def decode(self, steps: int) -> torch.Tensor:
+        check_positions(self._pos_host, steps, self.cfg.max_seq)
+        self._pos_host += steps
         out = torch.empty(steps, self.batch, dtype=torch.long, device=self.device)
         for i in range(steps):
             if self.graph is not None:
@@ -298,6 +332,52 @@ class GPTQDecoder:
             out[i].copy_(self.tokens)
         return out
 
+    def gather_logits(self) -> torch.Tensor:
+        """The latest logits over the whole vocabulary ``[B, vocab]`` (every rank gets them)."""
+        lg = self.last_logits
+        if self.world > 1:
+            parts = [torch.empty_like(lg) for _ in range(self.world)]
+            dist.all_gather(parts, lg.contiguous(), group=self.group)
+            lg = torch.cat(parts, dim=1)
+        return lg[:, :self.cfg.vocab]
+
     def bytes_per_token(self) -> int:
         """Bytes of weights this rank streams per decode step (packed linears + its lm_head slice)."""
         return sum(L.linear_bytes() for L in self.layers) + self.lm_head.numel() * 2
+
+
+@torch.no_grad()
+def tp_parity(cfg: DecoderConfig, prompt: torch.Tensor, device, fused_allreduce: bool = False) -> dict:
+    """Does the tensor-parallel model compute what the unsharded model computes?  Every rank of the default
+    process group builds its shard and runs the prompt plus one decode step; rank 0 also builds the whole model
+    and compares the logits over the full vocabulary.  The yardstick is the output contract of the path applied
+    to the vocabulary projection: ``1e-2 * ||h||_2 * max|w|`` per logit, h the final hidden state.  Returns
+    ``{max_abs_err, tol, ok}`` on rank 0 (``{}`` elsewhere)."""
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    batch = prompt.shape[0]
+    m = GPTQDecoder(cfg, batch=batch, device=device, fused_allreduce=fused_allreduce)
+    m.prefill(prompt)
+    lg_prompt = m.gather_logits()
+    ref = None
+    tok = torch.zeros(batch, dtype=torch.long, device=device)
+    if rank == 0:
+        ref = GPTQDecoder(cfg, batch=batch, device=device, single=True)
+        ref.prefill(prompt)
+        tok.copy_(ref.tokens)
+    if dist.is_initialized():
+        dist.broadcast(tok, src=0)
+    m.tokens.copy_(tok)           # both models continue from the same token even if a near-tie picked differently
+    m.decode(1)
+    lg_step = m.gather_logits()
+    if rank != 0:
+        return {}
+    ref_prompt = ref.last_logits[:, :cfg.vocab]
+    h = ref.last_hidden.float()
+    ref.decode(1)
+    ref_step = ref.last_logits[:, :cfg.vocab]
+    wmax = float(ref.lm_head.float().abs().max())
+    tol = 1e-2 * float(h.norm(dim=-1).min()) * wmax
+    finite = torch.isfinite(ref_prompt) & torch.isfinite(ref_step)
+    err = max(float(((lg_prompt - ref_prompt).abs() * finite).max()), float(((lg_step - ref_step).abs() * finite).max()))
+    return {"max_abs_err": err, "tol": tol, "ok": bool(err <= tol), "world": m.world,
+            "fused_allreduce": bool(fused_allreduce), "same_first_token": bool(torch.equal(m.tokens, ref.tokens))}

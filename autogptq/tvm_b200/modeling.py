@@ -12,6 +12,7 @@ Llama and OPT layer tables follow ``modeling/llama.py:4-12`` and ``modeling/opt.
 """
 from __future__ import annotations
 
+import contextlib
 import json
 import os
 from dataclasses import dataclass, asdict
@@ -79,6 +80,27 @@ def make_quant(model: nn.Module, names: List[str], bits: int, group_size: int) -
         setattr(parent, leaf, QuantLinear(bits, group_size, old.in_features, old.out_features, old.bias is not None))
 
 
+@contextlib.contextmanager
+def _parameters_on_meta():
+    """Build a model whose *parameters* take no memory while its buffers are created for real.
+
+    Buffers that are not part of a checkpoint (rotary ``inv_freq``, causal masks, QuantLinear's default
+    ``g_idx``) keep the values their modules compute at construction; a model built wholly on the meta device
+    and materialised with ``to_empty`` would leave them uninitialised."""
+    register = nn.Module.register_parameter
+
+    def register_on_meta(module, name, param):
+        register(module, name, param)
+        if param is not None and param.device.type != "meta":
+            module._parameters[name] = nn.Parameter(param.detach().to("meta"), requires_grad=param.requires_grad)
+
+    nn.Module.register_parameter = register_on_meta
+    try:
+        yield
+    finally:
+        nn.Module.register_parameter = register
+
+
 class GPTQModel(nn.Module):
     """Thin wrapper like the reference's ``BaseGPTQForCausalLM``: holds the model and its quantize config."""
 
@@ -133,7 +155,7 @@ class AutoGPTQForCausalLM:
         if not os.path.isfile(path):
             raise FileNotFoundError(f"Could not find model at {path}")
 
-        with torch.device("meta"):
+        with _parameters_on_meta():
             model = AutoModelForCausalLM.from_config(config, trust_remote_code=trust_remote_code, torch_dtype=torch.float16)
         ignore = [table["lm_head"]] + table["outside"]
         names = [n for n in find_layers(model) if not any(n.startswith(i) for i in ignore)]
@@ -144,15 +166,13 @@ class AutoGPTQForCausalLM:
             state = load_file(path)
         else:
             state = torch.load(path, map_location="cpu")
-        model.to_empty(device="cpu")                       # materialise what is still on the meta device
-        for name in names:                                  # QuantLinear buffers were created on CPU already
-            pass
-        missing, unexpected = model.load_state_dict(state, strict=False, assign=True)
-        tied = {table["lm_head"] + ".weight"}
-        missing = [m for m in missing if m not in tied and not m.endswith("rotary_emb.inv_freq")]
+        model.load_state_dict(state, strict=False, assign=True)
+        if getattr(config, "tie_word_embeddings", False):
+            model.tie_weights()                             # lm_head shares the embedding loaded above
+        # every parameter must have come from the checkpoint (buffers it does not hold keep their constructed values)
+        missing = [n for n, p_ in model.named_parameters() if p_.device.type == "meta"]
         if missing:
             raise RuntimeError(f"checkpoint lacks tensors: {missing[:5]}{' ...' if len(missing) > 5 else ''}")
-        model.tie_weights()
         model = model.to(device)
         for key in ("max_position_embeddings", "seq_length", "n_positions"):
             if hasattr(model.config, key):

@@ -80,6 +80,7 @@ class QuantLinear(nn.Module):
         self._qweight_run = None   # the weights the kernels read: qweight itself or its row-sorted copy
         self._g_idx_run = None     # None => rows use group k // groupsize
         self._x_perm = None        # None => no gather of x
+        self._gemm_ok = False      # the run-time layout meets the tensor-core kernel's one-group-per-32-rows rule
 
     # ---- offline packing (CPU) ----------------------------------------------------------
     def pack(self, linear, scales, zeros, g_idx=None):
@@ -142,6 +143,15 @@ class QuantLinear(nn.Module):
                 gs, (torch.arange(K, device=dev, dtype=torch.int64) // self.groupsize).to(torch.int32))
             self._qweight_run, self._x_perm = qs, perm
             self._g_idx_run = None if sorted_trivial else gs
+        # the tensor-core kernel takes one group per aligned 32-row block: true for every run-time g_idx built above
+        # (block-uniform or sorted by group with whole blocks) except a NULL g_idx with a group size that is no
+        # multiple of 32, and a sorted layout whose groups do not fill whole blocks
+        g_run = self._g_idx_run
+        if g_run is None:
+            self._gemm_ok = self.bits in (3, 4) and self.groupsize % 32 == 0
+        else:
+            b = g_run.view(K // 32, 32)
+            self._gemm_ok = self.bits in (3, 4) and bool((b == b[:, :1]).all().item())
         self._ready_for = (dev, self.qweight.data_ptr(), self.g_idx.data_ptr())
 
     def _ready(self) -> bool:
@@ -162,12 +172,13 @@ class QuantLinear(nn.Module):
         args = (self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize)
         if M <= GEMV_MAX_M:
             y = ops.gemv(x2, *args, **kw)
-        elif self.bits in (3, 4):
+        elif self._gemm_ok:
             # measured on B200: from 9 rows on, one tensor-core pass (35-45 us for a 4096 x 12288 layer) beats two
             # or more GEMV passes
             y = ops.gemm(x2, *args, **kw)
         else:
-            # 2- and 8-bit layers have no tensor-core kernel: GEMV passes of up to 8 rows
+            # 2- and 8-bit layers, and layers whose groups cut through 32-row blocks, have no tensor-core kernel:
+            # GEMV passes of up to 8 rows
             y = torch.empty((M, self.outfeatures), dtype=torch.float16, device=x2.device)
             for m0 in range(0, M, GEMV_MAX_M):
                 ops.gemv(x2[m0:m0 + GEMV_MAX_M], *args, out=y[m0:m0 + GEMV_MAX_M], **kw)

@@ -5,17 +5,29 @@ different devices, ``quantization/opt.py:270-304``); these are the slicing rules
 format imposes when one linear is split over ranks:
 
 * column-parallel (shard the output features N): take the same columns of ``qweight``, ``scales``
-  and ``bias`` and the matching packed words of ``qzeros`` (fields run along N, so the cut must fall
-  on a multiple of 32 columns); ``g_idx`` is shared.  Outputs are concatenated; no exchange.
-* row-parallel (shard the input features K): the cut falls on quantisation-group boundaries, so a
-  rank takes whole groups: rows ``[g_a*gs, g_b*gs)`` of ``qweight`` (32/bits rows per word),
-  rows ``[g_a, g_b)`` of ``scales`` and ``qzeros``, and a local ``g_idx``.  Outputs are summed
-  (one all-reduce); the bias is added by rank 0 only.  Needs ``g_idx[k] == k // gs``
-  (act-order layers are re-ordered before they are cut).
+  and ``bias`` and the matching packed words of ``qzeros`` (fields run along N, so every cut must fall
+  on a multiple of 32 columns); ``g_idx`` is shared.  Outputs are concatenated; no exchange.  A fused
+  layer (q|k|v, gate|up) is cut part by part, so that a rank owns the same heads / the same slice of
+  the FFN width in every part.
+* row-parallel (shard the input features K): a rank takes rows ``[k_a, k_b)`` of ``qweight`` (cuts on
+  multiples of 32 rows: 32 rows are ``bits`` whole words).  Outputs are summed (one all-reduce); the bias
+  is added by rank 0 only.  Two cases:
+
+  - ``g_idx[k] == k // group_size`` and both cuts on group boundaries: the shard is an ordinary layer of
+    its own -- rows ``[k_a/gs, k_b/gs)`` of ``scales`` / ``qzeros`` and a local ``g_idx``.
+  - anything else (act-order checkpoints, cuts through groups): the shard keeps the GLOBAL group ids of
+    its rows and the whole ``scales`` / ``qzeros``: every K shard of an act-order layer touches every
+    group (``W[k, n] = scales[g_idx[k], n] * (q[k, n] - zeros[g_idx[k], n])``, reference
+    ``auto_gptq/nn_modules/qlinear.py:242``).  Such a shard has few rows per group, so it runs on the
+    general GEMV kernel, not the streaming one.
+
+  (An act-order layer whose input is an element-wise function of a column-parallel layer's output -- fc1 -> fc2,
+  gate/up -> down -- could avoid that by re-ordering its rows by group once and applying the same permutation to
+  the producer's output columns at load time; that is not implemented.)
 """
 from __future__ import annotations
 
-from typing import List, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
@@ -30,39 +42,88 @@ def split_sizes(total: int, parts: int, unit: int) -> List[int]:
     return [(base + (1 if r < extra else 0)) * unit for r in range(parts)]
 
 
-def _bounds(sizes: List[int], rank: int) -> Tuple[int, int]:
+def bounds(sizes: Sequence[int], rank: int) -> Tuple[int, int]:
     a = sum(sizes[:rank])
     return a, a + sizes[rank]
 
 
-def shard_column(layer: PackedLayer, rank: int, world: int) -> PackedLayer:
-    a, b = _bounds(split_sizes(layer.N, world, 32), rank)
+def _group_size(layer: PackedLayer) -> int:
+    return layer.group_size if layer.group_size != -1 else layer.K
+
+
+def is_trivial(layer: PackedLayer) -> bool:
+    """``g_idx[k] == k // group_size``."""
+    gs = _group_size(layer)
+    return bool(torch.equal(layer.g_idx.long(), torch.arange(layer.K, device=layer.g_idx.device) // gs))
+
+
+def take_columns(layer: PackedLayer, ranges: Sequence[Tuple[int, int]]) -> PackedLayer:
+    """The layer restricted to the output columns ``[a, b)`` of every range, concatenated in order."""
+    cols, words = [], []
+    for a, b in ranges:
+        if a % 32 or b % 32 or not 0 <= a < b <= layer.N:
+            raise ValueError(f"column range [{a}, {b}) must be non-empty, inside the layer and cut on multiples of 32")
+        cols.append(torch.arange(a, b, device=layer.qweight.device))
+        words.append(torch.arange(a // 32 * layer.bits, b // 32 * layer.bits, device=layer.qweight.device))
+    c, w = torch.cat(cols), torch.cat(words)
+    return PackedLayer(layer.bits, layer.group_size, layer.K, int(c.numel()),
+                       layer.qweight.index_select(1, c).contiguous(), layer.qzeros.index_select(1, w).contiguous(),
+                       layer.scales.index_select(1, c).contiguous(), layer.g_idx.clone(),
+                       None if layer.bias is None else layer.bias.index_select(0, c).contiguous())
+
+
+def take_rows(layer: PackedLayer, k_a: int, k_b: int, keep_bias: bool) -> PackedLayer:
+    """The layer restricted to the input rows ``[k_a, k_b)`` (see the module docstring for the two cases)."""
+    if k_a % 32 or k_b % 32 or not 0 <= k_a < k_b <= layer.K:
+        raise ValueError(f"row range [{k_a}, {k_b}) must be non-empty, inside the layer and cut on multiples of 32")
+    gs = _group_size(layer)
+    ra, rb = k_a // 32 * layer.bits, k_b // 32 * layer.bits
+    bias = layer.bias if keep_bias else None
+    if is_trivial(layer) and k_a % gs == 0 and (k_b % gs == 0 or k_b == layer.K):
+        ga, gb = k_a // gs, -(-k_b // gs)
+        return PackedLayer(layer.bits, layer.group_size if layer.group_size != -1 else gs, k_b - k_a, layer.N,
+                           layer.qweight[ra:rb].contiguous(), layer.qzeros[ga:gb].contiguous(),
+                           layer.scales[ga:gb].contiguous(),
+                           (torch.arange(k_b - k_a, device=layer.g_idx.device) // gs).to(torch.int32), bias)
+    # global group ids, whole scales / qzeros
+    return PackedLayer(layer.bits, layer.group_size if layer.group_size != -1 else gs, k_b - k_a, layer.N,
+                       layer.qweight[ra:rb].contiguous(), layer.qzeros.contiguous(), layer.scales.contiguous(),
+                       layer.g_idx[k_a:k_b].contiguous(), bias)
+
+
+def shard_column(layer: PackedLayer, rank: int, world: int, parts: int = 1,
+                 sizes: Optional[Sequence[int]] = None) -> PackedLayer:
+    """Column-parallel shard.  ``parts`` > 1: the layer is ``parts`` equal blocks side by side (q|k|v, gate|up) and
+    the rank takes the same range of each.  ``sizes``: per-rank widths of one block (default: as even as possible
+    in multiples of 32)."""
+    if layer.N % parts:
+        raise ValueError("the layer's width is not a multiple of the number of fused parts")
+    width = layer.N // parts
+    if sizes is None:
+        sizes = split_sizes(width, world, 32)
+    a, b = bounds(sizes, rank)
     if a == b:
         raise ValueError("more ranks than 32-column blocks")
-    wa, wb = a // 32 * layer.bits, b // 32 * layer.bits
-    return PackedLayer(layer.bits, layer.group_size, layer.K, b - a,
-                       layer.qweight[:, a:b].contiguous(), layer.qzeros[:, wa:wb].contiguous(),
-                       layer.scales[:, a:b].contiguous(), layer.g_idx.clone(),
-                       None if layer.bias is None else layer.bias[a:b].contiguous())
+    return take_columns(layer, [(p * width + a, p * width + b) for p in range(parts)])
 
 
-def shard_row(layer: PackedLayer, rank: int, world: int) -> Tuple[PackedLayer, Tuple[int, int]]:
-    """Returns the shard and the range of input features ``[k_a, k_b)`` it consumes."""
-    gs = layer.group_size if layer.group_size != -1 else layer.K
-    if layer.K % gs != 0:
-        raise ValueError("row-parallel sharding needs K to be a multiple of group_size")
-    trivial = torch.arange(layer.K, device=layer.g_idx.device) // gs
-    if not torch.equal(layer.g_idx.long(), trivial):
-        raise ValueError("row-parallel sharding needs g_idx == k // group_size; re-order act-order layers first")
-    unit = gs if gs % 32 == 0 else gs * 32   # whole groups and whole packed words
-    k_a, k_b = _bounds(split_sizes(layer.K, world, unit), rank)
+def shard_row(layer: PackedLayer, rank: int, world: int,
+              sizes: Optional[Sequence[int]] = None) -> Tuple[PackedLayer, Tuple[int, int]]:
+    """Row-parallel shard and the range of input features ``[k_a, k_b)`` it consumes.  ``sizes``: per-rank row
+    counts (default: whole groups, as even as possible, when the layer's ``g_idx`` is ``k // group_size``;
+    multiples of 32 rows otherwise)."""
+    gs = _group_size(layer)
+    if sizes is None:
+        unit = 32
+        if is_trivial(layer) and layer.K % gs == 0:
+            unit = gs if gs % 32 == 0 else gs * 32
+            if layer.K % unit:
+                unit = 32
+        sizes = split_sizes(layer.K, world, unit)
+    k_a, k_b = bounds(sizes, rank)
     if k_a == k_b:
-        raise ValueError("more ranks than quantisation groups")
-    ra, rb = k_a // 32 * layer.bits, k_b // 32 * layer.bits
-    ga, gb = k_a // gs, k_b // gs
-    shard = PackedLayer(layer.bits, layer.group_size, k_b - k_a, layer.N,
-                        layer.qweight[ra:rb].contiguous(), layer.qzeros[ga:gb].contiguous(),
-                        layer.scales[ga:gb].contiguous(),
-                        (torch.arange(k_b - k_a, device=layer.g_idx.device) // gs).to(torch.int32),
-                        layer.bias if (layer.bias is not None and rank == 0) else None)
-    return shard, (k_a, k_b)
+        raise ValueError("more ranks than row blocks")
+    return take_rows(layer, k_a, k_b, keep_bias=(rank == 0)), (k_a, k_b)
+
+
+__all__ = ["split_sizes", "bounds", "is_trivial", "take_columns", "take_rows", "shard_column", "shard_row"]

@@ -172,8 +172,9 @@ B200GPTQ_API int b200gptq_sort_rows(const int32_t* qweight, const int32_t* g_idx
  *    B200GPTQ_ERR_TOO_LARGE.
  *  - All calls on one device share the array: calls that may overlap on the GPU race with each
  *    other; order them on one stream (or with events).
- *  - The first call on a device looks the array up and zero-fills its counters with synchronous
- *    runtime calls; make that call before any stream capture begins.
+ *  - The first call on a device looks the array's address up with a runtime call; make that call
+ *    before any stream capture begins.  (The array is zero-initialised storage and the kernels
+ *    leave their counters at zero, so nothing is cleared.)
  */
 B200GPTQ_API int b200gptq_gemv_static(const void* x, const int32_t* qweight, const int32_t* qzeros,
                          const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,

@@ -13,18 +13,24 @@ class _FakeCuda(torch.Tensor):
     is_cuda = property(lambda self: True)
 
 
-def _layer(bits):
-    m = ql.QuantLinear(bits, 128, 256, 64, False)
+def _layer(bits, groupsize=128):
+    m = ql.QuantLinear(bits, groupsize, 256, 64, False)
     m._ready = lambda: True
     m._qweight_run, m._g_idx_run, m._x_perm = m.qweight, None, None
+    m._gemm_ok = bits in (3, 4) and groupsize % 32 == 0
     return m
 
 
 @pytest.mark.parametrize("bits,M,want", [
     (4, 1, ["gemv:1"]), (4, 8, ["gemv:8"]), (4, 9, ["gemm:9"]), (3, 16, ["gemm:16"]), (4, 2048, ["gemm:2048"]),
     (8, 8, ["gemv:8"]), (8, 20, ["gemv:8", "gemv:8", "gemv:4"]), (2, 9, ["gemv:8", "gemv:1"]),
+    # a group size that cuts through 32-row blocks cannot use the tensor-core kernel (one group per block)
+    ((4, 16), 16, ["gemv:8", "gemv:8"]),
 ])
 def test_rows_decide_the_entry_point(monkeypatch, bits, M, want):
+    groupsize = 128
+    if isinstance(bits, tuple):
+        bits, groupsize = bits
     calls = []
 
     def fake(name):
@@ -37,6 +43,15 @@ def test_rows_decide_the_entry_point(monkeypatch, bits, M, want):
     monkeypatch.setattr(ql.ops, "gemm", fake("gemm"))
     monkeypatch.setattr(torch, "empty", lambda *a, device=None, **k: torch.zeros(*a, **k))
     x = torch.zeros((M, 256), dtype=torch.float16).as_subclass(_FakeCuda)
-    y = _layer(bits).forward(x)
+    y = _layer(bits, groupsize).forward(x)
     assert calls == want
     assert tuple(y.shape) == (M, 64)
+
+
+def test_decode_positions_are_checked_on_the_host():
+    from autogptq.tvm_b200.decoder import check_positions
+    check_positions(512, 256, 768)
+    with pytest.raises(ValueError):
+        check_positions(512, 257, 768)
+    with pytest.raises(ValueError):
+        check_positions(-1, 1, 768)

@@ -101,3 +101,21 @@ def test_gemm_full_size_against_dequantised_product(bits, M):
     assert bool((err <= tol).all())
     assert bool((err <= 2.0 ** -10 * ref.abs() + 0.02 * tol).all())
     _status_clear()
+
+
+def test_group_sizes_that_cut_through_row_blocks():
+    """The tensor-core kernel takes one group per aligned 32-row block.  A layer with group size 16 must be refused
+    by the entry point (not evaluated wrongly) and still run correctly through the module, which falls back to
+    GEMV passes."""
+    bits, K, N, gs, M = 4, 256, 128, 16, 16
+    layer = synth.make_layer(bits, K, N, gs, False, seed=5)
+    x = synth.make_x(M, K, seed=2)
+    _, _, W = O.dequantize(*_layer_np(layer), bits)
+    d = layer.to(DEV)
+    with pytest.raises(RuntimeError, match="32-row"):
+        ops.gemm(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs)
+    mod = QuantLinear(bits, gs, K, N, False)
+    mod.qweight, mod.qzeros, mod.scales, mod.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
+    mod = mod.to(DEV)
+    _check(mod(x.to(DEV)), x.numpy(), W)
+    assert mod._gemm_ok is False

@@ -13,23 +13,27 @@ if torch.cuda.is_available():
 
 
 def test_loaded_model_matches_dense_weights(tmp_path):
-    _tiny_llama_dir(tmp_path, bits=4, group_size=32, safetensors=True)
+    _, _, saved = _tiny_llama_dir(tmp_path, bits=4, group_size=32, safetensors=True)
     m = modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), device="cuda:0", use_safetensors=True, use_tvm=True)
     ids = torch.randint(0, 320, (1, 24), generator=torch.Generator().manual_seed(3)).to(DEV)
     with torch.no_grad():
         logits_q = m.model(input_ids=ids).logits.float()          # 24 rows: the tcgen05 GEMM path
         step_q = m.model(input_ids=ids[:, :1]).logits.float()     # 1 row: the GEMV path
-    # swap every QuantLinear for a dense layer built from the dequantise kernel's output
-    for name, mod in list(m.model.named_modules()):
+    # The yardstick is the model that was SAVED (constructed normally, never reloaded), with every QuantLinear
+    # swapped for a dense layer of the oracle's dequantised weights: a loader that damaged anything outside the
+    # linears (rotary tables, norms, embeddings) shows up as a difference.
+    from oracle import gptq_oracle as O
+    for name, mod in list(saved.named_modules()):
         if isinstance(mod, QuantLinear):
-            _, W = ops.dequantize(mod.qweight, mod.qzeros, mod.scales, mod.g_idx, mod.bits, mod.groupsize, want_q=False)
-            lin = torch.nn.Linear(mod.infeatures, mod.outfeatures, bias=False, device=DEV, dtype=torch.float16)
-            lin.weight.data = W.t().contiguous()
+            _, _, W = O.dequantize(mod.qweight.numpy(), mod.qzeros.numpy(), mod.scales.numpy(), mod.g_idx.numpy(), mod.bits)
+            lin = torch.nn.Linear(mod.infeatures, mod.outfeatures, bias=False, dtype=torch.float16)
+            lin.weight.data = torch.from_numpy(W).t().contiguous()
             parent, _, leaf = name.rpartition(".")
-            setattr(m.model.get_submodule(parent), leaf, lin)
+            setattr(saved.get_submodule(parent), leaf, lin)
+    saved = saved.to(DEV).eval()
     with torch.no_grad():
-        logits_d = m.model(input_ids=ids).logits.float()
-        step_d = m.model(input_ids=ids[:, :1]).logits.float()
+        logits_d = saved(input_ids=ids).logits.float()
+        step_d = saved(input_ids=ids[:, :1]).logits.float()
     assert (logits_q - logits_d).abs().max() <= 2e-2 * max(1.0, logits_d.abs().max().item())
     assert (step_q - step_d).abs().max() <= 2e-2 * max(1.0, step_d.abs().max().item())
     out = m.generate(input_ids=ids[:, :4], max_new_tokens=4, do_sample=False)

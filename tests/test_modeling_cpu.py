@@ -55,6 +55,29 @@ def test_from_quantized_round_trip(tmp_path, safetensors):
             assert torch.equal(getattr(a, buf), getattr(b, buf)), (n, buf)
     assert not isinstance(loaded.model.lm_head, QuantLinear)
     assert torch.equal(loaded.model.model.embed_tokens.weight, saved.model.embed_tokens.weight)
+    assert torch.equal(loaded.model.lm_head.weight, saved.lm_head.weight)
+    # buffers that no checkpoint holds must carry the values a normally constructed model computes
+    from transformers import LlamaForCausalLM
+    fresh = LlamaForCausalLM(cfg)
+    bufs, fresh_bufs = dict(loaded.model.named_buffers()), dict(fresh.named_buffers())
+    checked = 0
+    for name, ref in fresh_bufs.items():
+        if "inv_freq" in name:
+            assert torch.allclose(bufs[name].float(), ref.float()), name
+            checked += 1
+    assert checked >= 1
+    assert not any(p.device.type == "meta" for p in loaded.model.parameters())
+
+
+def test_missing_lm_head_is_reported(tmp_path):
+    """With untied embeddings a checkpoint without lm_head.weight must not load silently."""
+    _tiny_llama_dir(tmp_path, safetensors=False)
+    path = os.path.join(tmp_path, "gptq_model-4bit-32g.bin")
+    state = torch.load(path)
+    del state["lm_head.weight"]
+    torch.save(state, path)
+    with pytest.raises(RuntimeError, match="lacks tensors"):
+        modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), device="cpu", use_tvm=True)
 
 
 def test_other_backends_are_refused(tmp_path):

@@ -53,11 +53,26 @@ def _worker(rank, world, port, bits, K, N, gs):
         y_row = x[:, k_a:k_b] @ _dense(row) + (row.bias.float() if row.bias is not None else 0.0)
         dist.all_reduce(y_row)
         assert torch.allclose(y_row, want, atol=1e-3)
+        # row-parallel on an act-order layer: every shard keeps the global group ids of its rows and the whole
+        # scales / qzeros (W[k, n] = scales[g_idx[k], n] * (q[k, n] - zeros[g_idx[k], n]), qlinear.py:242)
+        act = synth.make_layer(bits, K, N, gs, True, bias=False, seed=6)
+        want_act = x @ _dense(act)
+        row, (k_a, k_b) = tp.shard_row(act, rank, world)
+        assert row.scales.shape == act.scales.shape and torch.equal(row.g_idx, act.g_idx[k_a:k_b])
+        y_row = x[:, k_a:k_b] @ _dense(row)
+        dist.all_reduce(y_row)
+        assert torch.allclose(y_row, want_act, atol=1e-3)
+        # a fused layer of three equal blocks (q|k|v): the rank owns the same columns of every block
+        if N % 96 == 0:
+            fused = tp.shard_column(full, rank, world, parts=3)
+            a, b = tp.bounds(tp.split_sizes(N // 3, world, 32), rank)
+            cols = torch.cat([torch.arange(p * (N // 3) + a, p * (N // 3) + b) for p in range(3)])
+            assert torch.allclose(x @ _dense(fused) + fused.bias.float(), want[:, cols], atol=1e-4)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("bits,K,N,gs", [(4, 512, 128, 128), (3, 768, 96, 128), (4, 256, 64, 64)])
+@pytest.mark.parametrize("bits,K,N,gs", [(4, 512, 128, 128), (3, 768, 192, 128), (4, 256, 64, 64)])
 def test_two_rank_sharding_matches_the_full_layer(bits, K, N, gs):
     mp.spawn(_worker, args=(2, _free_port(), bits, K, N, gs), nprocs=2, join=True)
 
@@ -68,5 +83,9 @@ def test_split_sizes_and_errors():
     with pytest.raises(ValueError):
         tp.split_sizes(100, 2, 32)
     act = synth.make_layer(4, 256, 64, 64, act_order=True, seed=1)
+    shard, (k_a, k_b) = tp.shard_row(act, 1, 2)
+    assert (k_a, k_b) == (128, 256) and shard.K == 128 and shard.scales.shape[0] == 4   # all groups stay
     with pytest.raises(ValueError):
-        tp.shard_row(act, 0, 2)
+        tp.take_rows(act, 16, 48, keep_bias=False)       # cuts must fall on multiples of 32 rows
+    with pytest.raises(ValueError):
+        tp.take_columns(act, [(0, 48)])                  # and on multiples of 32 columns
