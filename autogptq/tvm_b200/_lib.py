@@ -28,6 +28,15 @@ _SIGNATURES = {
     "b200gptq_gemm": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_sort_rows": (_c_int, [_c_void_p] * 3 + [_c_int] * 3 + [_c_void_p] * 3),
     "b200gptq_pack_fields": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]),
+    "b200gptq_tp_buffer_bytes": (_c_size_t, []),
+    "b200gptq_gemv_tp": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_void_p,
+                                  ctypes.c_longlong, _c_void_p]),
+    "b200gptq_tp_allreduce": (_c_int, [_c_void_p] * 2 + [_c_int] * 4 + [_c_void_p, ctypes.c_longlong, _c_void_p]),
+    "b200gptq_tp_status": (_c_int, [_c_void_p, _c_void_p, _c_void_p]),
+    "b200gptq_tp_enable_peer": (_c_int, [_c_int]),
+    "b200gptq_tp_open_peer": (_c_int, [_c_void_p, _c_void_p]),
+    "b200gptq_tp_close_peer": (_c_int, [_c_void_p]),
+    "b200gptq_tp_probe": (_c_int, [_c_void_p, _c_void_p]),
     "b200gptq_gemv_static": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p]),
     "b200gptq_gemv_static_capacity": (_c_size_t, []),
     "b200gptq_add_norm": (_c_int, [_c_void_p] * 5 + [_c_int, _c_int, ctypes.c_float, _c_int, _c_void_p]),

@@ -49,6 +49,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tp_exchange.cuh"
 
 namespace b200gptq {
 
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, MULTI ? 2 : 3)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
                    const __half* x, const int32_t* __restrict__ qzeros, const int32_t* __restrict__ x_perm,
                    const __half* __restrict__ bias, __half* __restrict__ y, int M_rows, int K, int N,
-                   int group_size, Plan plan, unsigned int* __restrict__ status) {
+                   int group_size, Plan plan, unsigned int* __restrict__ status, const __grid_constant__ TpArgs tp) {
     const int M = MULTI ? M_rows : 1;
     constexpr int MM = MULTI ? kMaxM : 1;
     using T = Traits<BITS>;
@@ -348,6 +349,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     __shared__ __align__(8) uint64_t bars[kMaxRing + 3];   // full[R] at 0, scales, combine, whole-x copy
     __shared__ unsigned int taken[kMaxRing];               // warps that have moved the unit in a ring slot to registers
     __shared__ volatile int gave_up;
+    __shared__ unsigned int tp_epoch;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int R = plan.ring_units, C = plan.cluster, S = plan.stage_units, GB = plan.group_box;
@@ -628,16 +630,25 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
     __syncthreads();
     const int n = cg * kCgCols + tid;
-    if (C == 1) {
+    // The column group's sums over all of K end up in v[] of ONE CTA (the only one of a group, or the cluster's
+    // first); `finish` adds the other ranks' sums (tensor-parallel row shards) and the bias and writes y.
+    auto finish = [&](float (&v)[MM]) {
+        if (tp.world > 1) tp_exchange_group<MM>(tp, cg, tid, M, v, &tp_epoch);
         if (n < N) {
 #pragma unroll
             for (int m = 0; m < MM; ++m)
                 if (m < M) {
-                    float v = part[m * kCgCols + tid] - corr[m];
-                    if (bias) v += __half2float(bias[n]);
-                    y[(size_t)m * N + n] = __float2half_rn(v);
+                    float o = v[m];
+                    if (bias) o += __half2float(bias[n]);
+                    y[(size_t)m * N + n] = __float2half_rn(o);
                 }
         }
+    };
+    float v[MM];
+    if (C == 1) {
+#pragma unroll
+        for (int m = 0; m < MM; ++m) v[m] = m < M ? part[m * kCgCols + tid] - corr[m] : 0.f;
+        finish(v);
         if (tid == 0 && gave_up) atomicExch(status + kStatusWord, 1u);
         return;
     }
@@ -653,16 +664,15 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                                          part[m * kCgCols + tid] - corr[m]);
         } else {
             mbar_wait(red_bar, 0, &gave_up);
-            if (n < N) {
 #pragma unroll
-                for (int m = 0; m < MM; ++m)
-                    if (m < M) {
-                        float v = part[m * kCgCols + tid] - corr[m];
-                        for (int r = 1; r < C; ++r) v += red[((r - 1) * M + m) * kCgCols + tid];
-                        if (bias) v += __half2float(bias[n]);
-                        y[(size_t)m * N + n] = __float2half_rn(v);
-                    }
+            for (int m = 0; m < MM; ++m) {
+                v[m] = 0.f;
+                if (m < M) {
+                    v[m] = part[m * kCgCols + tid] - corr[m];
+                    for (int r = 1; r < C; ++r) v[m] += red[((r - 1) * M + m) * kCgCols + tid];
+                }
             }
+            finish(v);
         }
         if (tid == 0 && gave_up) atomicExch(status + kStatusWord, 1u);
         return;
@@ -673,19 +683,21 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         for (int m = 0; m < MM; ++m)
             if (m < M) part[m * kCgCols + tid] -= corr[m];   // column tid is this thread's own
         cluster_sync_all();   // every CTA's partial result is in its `part`
-        if (rank == 0 && n < N) {
-#pragma unroll 1
-            for (int m = 0; m < M; ++m) {
-                // all remote reads are issued before the first is used; the sum stays in rank order
-                float rem[8];
+        if (rank == 0) {
 #pragma unroll
-                for (int r = 1; r < 8; ++r) rem[r] = r < C ? ld_cluster_f32(&part[m * kCgCols + tid], (uint32_t)r) : 0.f;
-                float v = part[m * kCgCols + tid];
+            for (int m = 0; m < MM; ++m) {
+                v[m] = 0.f;
+                if (m < M) {
+                    // all remote reads are issued before the first is used; the sum stays in rank order
+                    float rem[8];
 #pragma unroll
-                for (int r = 1; r < 8; ++r) v += rem[r];
-                if (bias) v += __half2float(bias[n]);
-                y[(size_t)m * N + n] = __float2half_rn(v);
+                    for (int r = 1; r < 8; ++r) rem[r] = r < C ? ld_cluster_f32(&part[m * kCgCols + tid], (uint32_t)r) : 0.f;
+                    v[m] = part[m * kCgCols + tid];
+#pragma unroll
+                    for (int r = 1; r < 8; ++r) v[m] += rem[r];
+                }
             }
+            finish(v);
         }
         cluster_sync_all();   // the other CTAs keep their shared memory alive until it has been read
     }
@@ -796,7 +808,7 @@ int set_smem_attr_once() {
 template <int BITS>
 int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                   const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int group_size,
-                  void* workspace, cudaStream_t stream, const int* knobs) {
+                  void* workspace, cudaStream_t stream, const int* knobs, const TpArgs* tp_args) {
     int smem_bytes = 0;
     const Plan plan = make_plan<BITS>(M, K, N, group_size, x_perm != nullptr, knobs, &smem_bytes);
     unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
@@ -844,8 +856,13 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
     cfg.numAttrs = 2;
     auto kernel = M == 1 ? (x_perm ? gemv_stream_kernel<BITS, false, true> : gemv_stream_kernel<BITS, false, false>)
                          : (x_perm ? gemv_stream_kernel<BITS, true, true> : gemv_stream_kernel<BITS, true, false>);
+    TpArgs tp = {};
+    if (tp_args) {
+        if (plan.cgs > kTpMaxGroups) return B200GPTQ_ERR_TOO_LARGE;
+        tp = *tp_args;
+    }
     B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmap_w, tmap_s, x, qzeros, x_perm, bias, y, M, K, N,
-                                         group_size, plan, status));
+                                         group_size, plan, status, tp));
     return B200GPTQ_OK;
 }
 
@@ -868,14 +885,21 @@ size_t gemv_stream_workspace_bytes(int M, int K, int N, int bits) {
 
 // `knobs` (NULL in the library's own calls) overrides plan heuristics; it exists for parameter sweeps that link
 // this translation unit directly.
+int gemv_stream_dispatch_tp(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
+                            const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int bits,
+                            int group_size, void* workspace, cudaStream_t stream, const int* knobs, const TpArgs* tp) {
+    if (bits == 4)
+        return launch_stream<4>(x, qweight, qzeros, scales, x_perm, bias, y, M, K, N, group_size, workspace, stream, knobs, tp);
+    if (bits == 3)
+        return launch_stream<3>(x, qweight, qzeros, scales, x_perm, bias, y, M, K, N, group_size, workspace, stream, knobs, tp);
+    return B200GPTQ_ERR_BITS;
+}
+
 int gemv_stream_dispatch_knobs(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                                const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int bits,
                                int group_size, void* workspace, cudaStream_t stream, const int* knobs) {
-    if (bits == 4)
-        return launch_stream<4>(x, qweight, qzeros, scales, x_perm, bias, y, M, K, N, group_size, workspace, stream, knobs);
-    if (bits == 3)
-        return launch_stream<3>(x, qweight, qzeros, scales, x_perm, bias, y, M, K, N, group_size, workspace, stream, knobs);
-    return B200GPTQ_ERR_BITS;
+    return gemv_stream_dispatch_tp(x, qweight, qzeros, scales, x_perm, bias, y, M, K, N, bits, group_size, workspace,
+                                   stream, knobs, nullptr);
 }
 
 int gemv_stream_dispatch(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,

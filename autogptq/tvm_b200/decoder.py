@@ -102,10 +102,12 @@ class DecoderLayer:
         self.qkv = _to_module(tp.shard_column(full, rank, world, parts=3, sizes=head_sizes), device)
         full = _full_layer(cfg, cfg.hidden, cfg.hidden, bias, seed + 2, device)
         self.o = _to_module(tp.shard_row(full, rank, world, sizes=head_sizes)[0], device)
+        self.o.tp_bias = full.bias          # the fused all-reduce adds the whole bias on every rank
         full = _full_layer(cfg, cfg.hidden, up_parts * cfg.inter, bias, seed + 3, device)
         self.up = _to_module(tp.shard_column(full, rank, world, parts=up_parts, sizes=inter_sizes), device)
         full = _full_layer(cfg, cfg.inter, cfg.hidden, bias, seed + 4, device)
         self.down = _to_module(tp.shard_row(full, rank, world, sizes=inter_sizes)[0], device)
+        self.down.tp_bias = full.bias
         del full
         g = torch.Generator(device=device).manual_seed(seed + 5)
         self.norm1_w = 1.0 + 0.01 * torch.randn(cfg.hidden, generator=g, device=device, dtype=torch.float16)
@@ -143,8 +145,16 @@ class GPTQDecoder:
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized() and not single) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.last_logits: Optional[torch.Tensor] = None   # this rank's slice of the latest logits [B, vocab_local]
+        # fused_allreduce: the row-parallel linears and the token pick exchange through peer memory inside the
+        # library's kernels instead of calling the process group (up to 8 rows; more rows still use it)
+        self.exchange = None
+        if fused_allreduce and self.world > 1:
+            from .exchange import PeerExchange
+            self.exchange = PeerExchange(self.device, group)
         dev = self.device
         self.layers = [DecoderLayer(cfg, i, self.rank, self.world, dev) for i in range(cfg.layers)]
+        for L in self.layers:
+            L.o.exchange = L.down.exchange = self.exchange
         g = torch.Generator(device=dev).manual_seed(7)   # replicated tensors: the same seed on every rank
         self.embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=g, device=dev)).half()
         self.pos_embed = None
@@ -189,6 +199,14 @@ class GPTQDecoder:
             dist.all_reduce(t, group=self.group)
         return t
 
+    def _row(self, mod: QuantLinear, x):
+        """A row-parallel linear: this rank's slice of the input in, the sum over ranks out."""
+        if self.world == 1:
+            return mod(x)
+        if self.exchange is not None:
+            return mod.forward_reduce(x)
+        return self._all_reduce(mod(x))          # the shard of rank 0 carries the bias
+
     def _rope(self, t, cos, sin):
         # t: [B, H, S, hd]; cos/sin: [S, hd/2]
         t1, t2 = t[..., 0::2], t[..., 1::2]
@@ -214,14 +232,14 @@ class GPTQDecoder:
         else:
             att = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         att = att.transpose(1, 2).reshape(B * S, L.heads_local * hd)
-        x = x + self._all_reduce(L.o(att)).reshape(B, S, cfg.hidden)
+        x = x + self._row(L.o, att).reshape(B, S, cfg.hidden)
         h = self._norm(x, L.norm2_w, L.norm2_b)
         u = L.up(h.reshape(B * S, cfg.hidden))
         if cfg.arch == "llama":
             act = F.silu(u[:, :L.inter_local]) * u[:, L.inter_local:]
         else:
             act = F.relu(u)
-        x = x + self._all_reduce(L.down(act.contiguous())).reshape(B, S, cfg.hidden)
+        x = x + self._row(L.down, act.contiguous()).reshape(B, S, cfg.hidden)
         return x
 
     def _embed(self, tokens, pos_idx):
@@ -243,7 +261,23 @@ class GPTQDecoder:
         self.last_logits = logits
         val, idx = logits.max(dim=-1)
         idx = idx + self.rank * self.vocab_local
-        if self.world > 1:
+        if self.world > 1 and self.exchange is not None and logits.shape[0] <= 8:
+            # every rank's best (logit, token) through the peer-memory exchange: a sum over ranks of vectors that are
+            # zero outside the rank's own slots is a gather; the numbers travel as pairs of fp16 values that are
+            # exact (logit = hi + lo, token = 256 * hi + lo)
+            B = logits.shape[0]
+            slots = torch.zeros((B, 4 * self.world), dtype=torch.float16, device=logits.device)
+            hi = val.half()
+            mine = slots[:, 4 * self.rank:4 * self.rank + 4]
+            mine[:, 0] = hi
+            mine[:, 1] = (val - hi.float()).half()
+            mine[:, 2] = (idx // 256).half()
+            mine[:, 3] = (idx % 256).half()
+            ops.tp_allreduce(slots, self.exchange)
+            got = slots.float().reshape(B, self.world, 4)
+            best = (got[:, :, 0] + got[:, :, 1]).argmax(dim=1, keepdim=True)
+            idx = (got[:, :, 2] * 256 + got[:, :, 3]).gather(1, best)[:, 0].long()
+        elif self.world > 1:
             vals = [torch.empty_like(val) for _ in range(self.world)]
             idxs = [torch.empty_like(idx) for _ in range(self.world)]
             dist.all_gather(vals, val, group=self.group)
@@ -291,12 +325,12 @@ class GPTQDecoder:
             ops.rope_cache(qkv, self.cos, self.sin, self.pos, q, L.k_cache, L.v_cache, L.heads_local, hd, rms)
             att = torch.empty_like(q)
             ops.attn_decode(q, L.k_cache, L.v_cache, self.pos, att, L.heads_local, hd)
-            o = self._all_reduce(L.o(att))
+            o = self._row(L.o, att)
             ops.add_norm(x, o, L.norm2_w, L.norm2_b, h, eps, rms)
             u = L.up(h)
             a = torch.empty((B, L.inter_local), dtype=torch.float16, device=self.device)
             ops.act(u, a, L.inter_local, rms)
-            delta = self._all_reduce(L.down(a))
+            delta = self._row(L.down, a)
         ops.add_norm(x, delta, self.final_norm_w, self.final_norm_b, h, eps, rms)
         self.last_hidden = h
         logits = h @ self.lm_head

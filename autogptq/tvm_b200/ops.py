@@ -151,6 +151,47 @@ def gemm(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=Non
                    group_size, out, workspace)
 
 
+def gemv_tp(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, exchange, bias=None, x_perm=None,
+            out=None, workspace=None):
+    """Row-parallel decode GEMV with the sum over ranks fused in (``b200gptq_gemv_tp``): ``x`` is this rank's slice of
+    the input ``[M<=8, K_local]``, the packed buffers are this rank's shard, ``bias`` is the full bias (the same on
+    every rank).  ``exchange`` is a :class:`exchange.PeerExchange`.  Returns the complete result on every rank."""
+    _need_cuda("x", x, torch.float16)
+    _need_cuda("qweight", qweight, torch.int32)
+    _need_cuda("qzeros", qzeros, torch.int32)
+    _need_cuda("scales", scales, torch.float16)
+    for name, t, dt in (("g_idx", g_idx, torch.int32), ("x_perm", x_perm, torch.int32), ("bias", bias, torch.float16)):
+        if t is not None:
+            _need_cuda(name, t, dt)
+    K, N = layer_dims(qweight, bits)
+    if x.dim() != 2 or x.shape[1] != K:
+        raise ValueError(f"x must be [M, {K}], got {tuple(x.shape)}")
+    M = x.shape[0]
+    dev = x.device
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    if workspace is None:
+        workspace = get_workspace(dev, _lib.workspace_bytes(_lib.OP_GEMV, M, K, N, bits))
+    with torch.cuda.device(dev):
+        st = _lib.lib.b200gptq_gemv_tp(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), _ptr(x_perm),
+                                       _ptr(bias), _ptr(out), M, K, N, bits, group_size, _ptr(workspace),
+                                       workspace.numel() * workspace.element_size(), exchange.rank, exchange.world,
+                                       exchange.peer_table, exchange.timeout_cycles, _stream(dev))
+    _lib.check(st, "b200gptq_gemv_tp")
+    return out
+
+
+def tp_allreduce(y, exchange, bias=None):
+    """In place ``y[M<=8, N] = sum over ranks of y (+ bias)`` through the peer-memory exchange."""
+    _need_cuda("y", y, torch.float16)
+    M, N = y.shape
+    with torch.cuda.device(y.device):
+        st = _lib.lib.b200gptq_tp_allreduce(_ptr(y), _ptr(bias), M, N, exchange.rank, exchange.world,
+                                            exchange.peer_table, exchange.timeout_cycles, _stream(y.device))
+    _lib.check(st, "b200gptq_tp_allreduce")
+    return y
+
+
 def gemv_static(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None, out=None):
     """Decode GEMV through ``b200gptq_gemv_static``: same results as :func:`gemv`, but the kernels'
     scratch is the fixed array inside the library, so nothing is allocated for the call except (when

@@ -81,6 +81,11 @@ class QuantLinear(nn.Module):
         self._g_idx_run = None     # None => rows use group k // groupsize
         self._x_perm = None        # None => no gather of x
         self._gemm_ok = False      # the run-time layout meets the tensor-core kernel's one-group-per-32-rows rule
+        # Row-parallel shard of a tensor-parallel model: forward_reduce() returns the sum over ranks.  `exchange` is an
+        # exchange.PeerExchange (fused all-reduce for up to 8 rows), `tp_bias` the full bias that every rank adds after
+        # the sum.
+        self.exchange = None
+        self.tp_bias = None
 
     # ---- offline packing (CPU) ----------------------------------------------------------
     def pack(self, linear, scales, zeros, g_idx=None):
@@ -183,6 +188,32 @@ class QuantLinear(nn.Module):
             for m0 in range(0, M, GEMV_MAX_M):
                 ops.gemv(x2[m0:m0 + GEMV_MAX_M], *args, out=y[m0:m0 + GEMV_MAX_M], **kw)
         return y.reshape(out_shape)
+
+    def forward_reduce(self, x):
+        """Row-parallel forward: this rank's slice of the input in, the complete output (summed over ranks) out.
+        Up to 8 rows go through ``b200gptq_gemv_tp`` (sum fused into the kernel, peer memory); more rows use the
+        process group's all-reduce."""
+        if self.exchange is None:
+            raise RuntimeError("forward_reduce needs an exchange (see exchange.PeerExchange)")
+        if not self._ready():
+            self.post_init()
+        x2 = x.half().reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if x2.shape[0] <= GEMV_MAX_M:
+            y = ops.gemv_tp(x2, self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize,
+                            self.exchange, bias=self.tp_bias, x_perm=self._x_perm)
+        else:
+            import torch.distributed as dist
+            saved, self.bias = self.bias, None
+            try:
+                y = self.forward(x2)
+            finally:
+                self.bias = saved
+            dist.all_reduce(y, group=self.exchange.group)
+            if self.tp_bias is not None:
+                y = y + self.tp_bias
+        return y.reshape(x.shape[:-1] + (self.outfeatures,))
 
     def extra_repr(self):
         return (f"in={self.infeatures}, out={self.outfeatures}, bits={self.bits}, "

@@ -184,6 +184,61 @@ B200GPTQ_API int b200gptq_gemv_static(const void* x, const int32_t* qweight, con
 B200GPTQ_API size_t b200gptq_gemv_static_capacity(void);
 
 /*
+ * Tensor-parallel row shards (one process per GPU of one node): the decode GEMV of a K shard with the sum
+ * over ranks fused into its last step, and that sum as a call of its own.
+ *
+ * The reference has no tensor parallelism (its only multi-GPU code places whole decoder layers on
+ * different devices, quantization/opt.py:270-304); these entry points serve the linears that a
+ * tensor-parallel split makes row-parallel -- o_proj / down_proj (auto_gptq/modeling/llama.py:8-12),
+ * out_proj / fc2 (auto_gptq/modeling/opt.py:11-16) -- whose per-rank results
+ *     y_r = x[:, rows of rank r] @ W[rows of rank r, :]          (arithmetic of qlinear.py:197-243)
+ * must be added up.  At decode sizes (8..18 KB per rank) that sum is pure latency, so instead of a
+ * collective library call every rank PUSHES its fp32 partial sums into every rank's exchange buffer
+ * with plain stores over NVLink, raises a counter there, waits on its own memory until all ranks'
+ * counters arrived and adds the slots in rank order (every rank gets the same bits; peers are never
+ * read; no multicast).
+ *
+ * Exchange buffers: every rank allocates b200gptq_tp_buffer_bytes() bytes of device memory (256-byte
+ * aligned), zero-fills them ONCE, and makes them addressable by all ranks of the node (CUDA IPC,
+ * cuMem fabric / POSIX handles, or torch symmetric memory) with peer access enabled; `peer_buffers`
+ * is a HOST array of `world` device pointers, entry r = rank r's buffer as mapped in the calling
+ * process (entry `rank` = the own buffer).  All ranks must issue the same sequence of calls with the
+ * same M and N.  Limits: world <= 8, M <= 8, N <= 16384.
+ *
+ * Waits are bounded: a rank that does not see a peer's counter within `timeout_cycles` GPU clock
+ * cycles (<= 0: 2e9) raises the sticky status word at byte 0 of its own buffer to 2, finishes with
+ * undefined results and returns control; b200gptq_tp_status() reads the word (it synchronises the
+ * stream).  Counters only grow, so the calls can be captured in a CUDA graph and replayed.
+ *
+ *   b200gptq_gemv_tp       y = sum over ranks of (x_r @ W_r) + bias; same arguments as b200gptq_gemv
+ *                          for this rank's shard.  `bias` (full, the same on every rank) is added
+ *                          after the sum.  With g_idx == NULL the exchange runs inside the GEMV
+ *                          kernel's combine step; shards that need the general kernel (act-order
+ *                          row shards keep global group ids) run it as a second kernel.
+ *   b200gptq_tp_allreduce  y[M, N] (fp16, in place) = sum over ranks of y + bias: the same exchange
+ *                          for partial results produced elsewhere.
+ */
+B200GPTQ_API size_t b200gptq_tp_buffer_bytes(void);
+B200GPTQ_API int b200gptq_gemv_tp(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                     const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
+                     int M, int K, int N, int bits, int group_size,
+                     void* workspace, size_t workspace_bytes,
+                     int rank, int world, void* const* peer_buffers, long long timeout_cycles, void* stream);
+B200GPTQ_API int b200gptq_tp_allreduce(void* y, const void* bias, int M, int N, int rank, int world,
+                          void* const* peer_buffers, long long timeout_cycles, void* stream);
+B200GPTQ_API int b200gptq_tp_status(const void* own_buffer, void* stream, unsigned int* host_out);
+/* Let kernels of the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess; fine if it
+ * is enabled already).  A host-side set-up call: once per peer before the first exchange. */
+B200GPTQ_API int b200gptq_tp_enable_peer(int peer_device);
+/* Set-up helpers for exchange buffers shared through CUDA IPC: map the allocation behind a 64-byte
+ * cudaIpcMemHandle_t (exported by the owning process with cudaIpcGetMemHandle) into the CURRENT device's address
+ * space (`*mapped` = base of that allocation; peer access to the owning device is enabled on the way), unmap it,
+ * and read one word through the runtime to check a mapping before kernels use it. */
+B200GPTQ_API int b200gptq_tp_open_peer(const void* ipc_handle, void** mapped);
+B200GPTQ_API int b200gptq_tp_close_peer(void* mapped);
+B200GPTQ_API int b200gptq_tp_probe(const void* device_ptr, unsigned int* host_out);
+
+/*
  * Decode-step helpers around the linears (fp16 storage, fp32 arithmetic, one launch each).  The
  * reference has no counterpart: it leaves everything between its QuantLinear calls to the
  * transformers modules (end2end/autogptq-generation-inference-benchmark.py:26-49).  They exist so
