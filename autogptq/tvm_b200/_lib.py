@@ -24,13 +24,14 @@ _SIGNATURES = {
     "b200gptq_dequant": (_c_int, [_c_void_p] * 4 + [_c_int] * 4 + [_c_void_p] * 3),
     "b200gptq_workspace_bytes": (_c_size_t, [_c_int] * 5),
     "b200gptq_gemv": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
+    "b200gptq_gemv_tuned": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_void_p]),
     "b200gptq_gemv_path": (_c_int, [_c_int] * 6),
     "b200gptq_gemm": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_sort_rows": (_c_int, [_c_void_p] * 3 + [_c_int] * 3 + [_c_void_p] * 3),
     "b200gptq_pack_fields": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]),
     "b200gptq_tp_buffer_bytes": (_c_size_t, []),
     "b200gptq_gemv_tp": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_void_p,
-                                  ctypes.c_longlong, _c_void_p]),
+                                  ctypes.c_longlong, _c_int, _c_int, _c_void_p]),
     "b200gptq_tp_allreduce": (_c_int, [_c_void_p] * 2 + [_c_int] * 4 + [_c_void_p, ctypes.c_longlong, _c_void_p]),
     "b200gptq_tp_status": (_c_int, [_c_void_p, _c_void_p, _c_void_p]),
     "b200gptq_tp_enable_peer": (_c_int, [_c_int]),

@@ -35,6 +35,8 @@ bool gemv_stream_supported(int M, int K, int N, int bits, int group_size);
 size_t gemv_stream_workspace_bytes(int M, int K, int N, int bits);
 int gemv_stream_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*,
                          const int32_t*, const __half*, __half*, int, int, int, int, int, void*, cudaStream_t);
+int gemv_stream_dispatch_knobs(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*,
+                               const __half*, __half*, int, int, int, int, int, void*, cudaStream_t, const int*);
 size_t gemm_workspace_bytes(int M, int K, int N, int bits);
 int gemm_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*, const int32_t*,
                   const __half*, __half*, int, int, int, int, int, void*, size_t, cudaStream_t);
@@ -127,6 +129,15 @@ int b200gptq_gemv_path(int M, int K, int N, int bits, int group_size, int has_g_
 int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
                   const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
                   int bits, int group_size, void* workspace, size_t workspace_bytes, void* stream) {
+    return b200gptq_gemv_tuned(x, qweight, qzeros, scales, g_idx, x_perm, bias, y, M, K, N, bits, group_size,
+                               workspace, workspace_bytes, 0, 0, stream);
+}
+
+int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                        const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
+                        int bits, int group_size, void* workspace, size_t workspace_bytes, int slices_per_sm,
+                        int ctas_per_sm, void* stream) {
+    if (slices_per_sm < 0 || slices_per_sm > 8 || ctas_per_sm < 0 || ctas_per_sm > 4) return B200GPTQ_ERR_SHAPE;
     if (!x || !qweight || !qzeros || !scales || !y) return B200GPTQ_ERR_NULL_POINTER;
     if (int st = check_layer(K, N, bits, &group_size)) return st;
     if (M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
@@ -136,10 +147,13 @@ int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, 
         return B200GPTQ_ERR_WORKSPACE;
     if (!aligned16(workspace)) return B200GPTQ_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size))
-        return gemv_stream_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
-                                    g_idx, x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K,
-                                    N, bits, group_size, workspace, st);
+    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size)) {
+        const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
+        return gemv_stream_dispatch_knobs(static_cast<const __half*>(x), qweight, qzeros,
+                                          static_cast<const __half*>(scales), x_perm, static_cast<const __half*>(bias),
+                                          static_cast<__half*>(y), M, K, N, bits, group_size, workspace, st,
+                                          (slices_per_sm || ctas_per_sm) ? knobs : nullptr);
+    }
     return gemv_generic_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
                                  g_idx, x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K, N,
                                  bits, group_size, workspace, st);

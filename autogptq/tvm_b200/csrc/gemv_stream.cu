@@ -291,7 +291,8 @@ struct Plan {
     int ring_units;   // unit buffers in the shared-memory ring
     int group_box;    // groups of scales / zero-points held per stage (rows of the scales TMA box)
     int push;         // 1: the K slices are combined by pushing partial sums into the first CTA's shared memory
-    int xfull;        // 1: the whole of x is copied to shared memory before it is gathered (layers with x_perm)
+    int xfull;        // x is bulk-copied to shared memory before it is re-ordered (the whole of x for layers with x_perm,
+                      // the CTA's rows otherwise): 2 into bytes of its own, 1 into the bytes of the partial sums, 0 not
     int early;        // when dependents may be launched: 0 once this CTA has passed its own wait, 1 as soon as it runs,
                       // 2 once all its weights are requested
 };
@@ -373,8 +374,14 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // CTA has arrived at the cluster barrier, which it does once its last fragment of x is staged.
     float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ps) + ps_bytes(S, M));
     float* red = part + M * kCgCols;
-    const unsigned short* xfull = reinterpret_cast<const unsigned short*>(part);
-    const bool use_xfull = PERM && plan.xfull != 0;
+    // x as copied from global memory: the whole of x for layers with a gather, the CTA's own rows otherwise; either
+    // in bytes of its own behind `red` (plan.xfull == 2) or, when it is larger, in the bytes of `part` / `red`
+    const bool use_xfull = plan.xfull != 0;
+    const bool xfull_aliased = plan.xfull == 1;
+    const unsigned short* xfull = reinterpret_cast<const unsigned short*>(
+        xfull_aliased ? part : red + (plan.push ? (plan.cluster - 1) * M * kCgCols : 0));
+    const int xrow_halves = PERM ? K : (kb_end - kb_begin) * kUnitRows;    // halves per row of x in the copy
+    const int xrow_first = PERM ? 0 : kb_begin * kUnitRows;                // first row of K held by the copy
 
     const int units_per_group = group_size / kUnitRows;
 
@@ -407,7 +414,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     __syncthreads();
     // matched by the wait in front of the first store into another CTA; a CTA that gathers x through `part` / `red`
     // arrives only when it has finished with those bytes
-    if (push && !use_xfull) cluster_arrive();
+    if (push && !xfull_aliased) cluster_arrive();
     if (plan.early == 1) asm volatile("griddepcontrol.launch_dependents;");
 
     const int g = lane >> 2, j = lane & 3;
@@ -506,11 +513,13 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                     // L2 lines at the same moment; one linear bulk copy of x per CTA and a gather from shared memory
                     // costs the L2 a twelfth of the requests.
                     if (tid == 0) {
-                        const uint32_t bytes = (uint32_t)(M * K * 2);
-                        mbar_arrive_expect_tx(x_bar, bytes);
-                        asm volatile(
-                            "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                            ::"r"(smem_u32(xfull)), "l"(x), "r"(bytes), "r"(x_bar) : "memory");
+                        const uint32_t row_bytes = (uint32_t)(xrow_halves * 2);
+                        mbar_arrive_expect_tx(x_bar, row_bytes * (uint32_t)M);
+                        for (int mm = 0; mm < M; ++mm)
+                            asm volatile(
+                                "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                ::"r"(smem_u32(xfull) + mm * row_bytes), "l"(x + (size_t)mm * K + xrow_first),
+                                  "r"(row_bytes), "r"(x_bar) : "memory");
                     }
                     mbar_wait(x_bar, 0, &gave_up);
                 }
@@ -518,7 +527,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             unsigned short xv[8];
             if (use_xfull) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) xv[i] = active ? xfull[m * K + kx[i]] : (unsigned short)0;
+                for (int i = 0; i < 8; ++i) xv[i] = active ? xfull[m * xrow_halves + kx[i] - xrow_first] : (unsigned short)0;
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) xv[i] = active ? __ldcg(xu + (size_t)m * K + kx[i]) : (unsigned short)0;
@@ -548,7 +557,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
         __syncthreads();   // fragments and sums are in shared memory
         first = false;
-        if (push && use_xfull && kb_b == kb_end) cluster_arrive();
+        if (push && xfull_aliased && kb_b == kb_end) cluster_arrive();
 
         // ---- the units of this stage ----
         int gl = 0;                                                            // group of the current unit, relative to g0
@@ -758,10 +767,15 @@ Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* kn
     p.group_box = max_groups_per_stage(p, group_size);
     p.push = (c > 1 && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
     p.early = (knobs && knobs[3] > 0) ? knobs[3] - 1 : 0;
-    // layers with a gather: stage the whole of x when it is small enough (knobs[4] == 1 switches it off)
-    p.xfull = (has_perm && M * K * 2 <= kXFullMax && !(knobs && knobs[4] == 1)) ? 1 : 0;
+    // layers with a gather take x through a linear bulk copy when it is small enough (knobs[4] == 1 switches it
+    // off): small copies get bytes of their own, larger ones share the bytes of the partial sums (the CTA then joins
+    // its cluster's barrier only when it has finished with x).  Without a gather a CTA reads only its own rows of x,
+    // and plain loads measured faster than the copy.
+    const int xcopy_bytes = M * (has_perm ? K : longest * kUnitRows) * 2;
+    p.xfull = (!has_perm || (knobs && knobs[4] == 1)) ? 0 : (xcopy_bytes <= 4096 ? 2 : (xcopy_bytes <= kXFullMax ? 1 : 0));
     int tail = part_bytes(M) + (p.push ? red_bytes(M, c) : 0);
-    if (p.xfull && tail < M * K * 2) tail = M * K * 2;   // x as copied shares the bytes of the partial sums
+    if (p.xfull == 2) tail += xcopy_bytes;
+    if (p.xfull == 1 && tail < xcopy_bytes) tail = xcopy_bytes;
     const int fixed = xs_bytes(p.stage_units, M) + s_sm_bytes(p.group_box) + z_sm_bytes(p.group_box) +
                       ps_bytes(p.stage_units, M) + tail + 1024;
     // Footprint: as many CTAs per SM as still let a CTA hold its whole slice (at least two); CTAs of the next launch
@@ -883,8 +897,8 @@ size_t gemv_stream_workspace_bytes(int M, int K, int N, int bits) {
     return kCounterBytes;  // only the status word: partial sums travel through distributed shared memory
 }
 
-// `knobs` (NULL in the library's own calls) overrides plan heuristics; it exists for parameter sweeps that link
-// this translation unit directly.
+// `knobs` (NULL = the defaults) overrides plan heuristics: b200gptq_gemv_tuned passes the first two, parameter sweeps
+// that link this translation unit directly use all of them.
 int gemv_stream_dispatch_tp(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                             const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int bits,
                             int group_size, void* workspace, cudaStream_t stream, const int* knobs, const TpArgs* tp) {

@@ -43,7 +43,7 @@ int fill_tp(TpArgs* tp, int rank, int world, void* const* peers, long long timeo
     if (!peers) return B200GPTQ_ERR_NULL_POINTER;
     tp->rank = rank;
     tp->world = world;
-    tp->timeout = timeout_cycles > 0 ? timeout_cycles : 2000000000LL;
+    tp->timeout = timeout_cycles > 0 ? timeout_cycles : 20000000000LL;   // ~10 s: ranks may be seconds apart at start-up
     for (int p = 0; p < kTpMaxWorld; ++p) tp->peer[p] = nullptr;
     for (int p = 0; p < world; ++p) {
         if (!peers[p]) return B200GPTQ_ERR_NULL_POINTER;
@@ -91,7 +91,10 @@ int b200gptq_tp_allreduce(void* y, const void* bias, int M, int N, int rank, int
 int b200gptq_gemv_tp(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
                      const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
                      int bits, int group_size, void* workspace, size_t workspace_bytes, int rank, int world,
-                     void* const* peer_buffers, long long timeout_cycles, void* stream) {
+                     void* const* peer_buffers, long long timeout_cycles, int slices_per_sm, int ctas_per_sm,
+                     void* stream) {
+    if (slices_per_sm < 0 || slices_per_sm > 8 || ctas_per_sm < 0 || ctas_per_sm > 4) return B200GPTQ_ERR_SHAPE;
+    const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
     if (!x || !qweight || !qzeros || !scales || !y) return B200GPTQ_ERR_NULL_POINTER;
     if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return B200GPTQ_ERR_BITS;
     if (K <= 0 || N <= 0 || K % 32 != 0 || N % 32 != 0 || M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
@@ -107,7 +110,8 @@ int b200gptq_gemv_tp(const void* x, const int32_t* qweight, const int32_t* qzero
     if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size))
         return gemv_stream_dispatch_tp(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
                                        x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K, N, bits,
-                                       group_size, workspace, s, nullptr, world > 1 ? &tp : nullptr);
+                                       group_size, workspace, s, (slices_per_sm || ctas_per_sm) ? knobs : nullptr,
+                                       world > 1 ? &tp : nullptr);
     // general kernel: this rank's sums first (without the bias), then the exchange as a kernel of its own
     if (int st = gemv_generic_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
                                        g_idx, x_perm, world > 1 ? nullptr : static_cast<const __half*>(bias),

@@ -103,7 +103,7 @@ def sort_rows(qweight, g_idx, bits: int):
 
 
 def _matmul(fn_name: str, op: int, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits, group_size,
-            out, workspace):
+            out, workspace, tuning=None):
     _need_cuda("x", x, torch.float16)
     _need_cuda("qweight", qweight, torch.int32)
     _need_cuda("qzeros", qzeros, torch.int32)
@@ -129,19 +129,27 @@ def _matmul(fn_name: str, op: int, x, qweight, qzeros, scales, g_idx, x_perm, bi
     if workspace is None:
         workspace = get_workspace(dev, need)
     with torch.cuda.device(dev):
-        st = getattr(_lib.lib, fn_name)(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
-                                        _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
-                                        _ptr(workspace), workspace.numel() * workspace.element_size(),
-                                        _stream(dev))
+        if tuning is not None:
+            fn_name = "b200gptq_gemv_tuned"
+            st = _lib.lib.b200gptq_gemv_tuned(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
+                                              _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
+                                              _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                              int(tuning[0]), int(tuning[1]), _stream(dev))
+        else:
+            st = getattr(_lib.lib, fn_name)(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
+                                            _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
+                                            _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                            _stream(dev))
     _lib.check(st, fn_name)
     return out
 
 
 def gemv(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None,
-         out=None, workspace=None):
-    """Decode GEMV, ``x`` fp16 ``[M<=8, K]`` -> fp16 ``[M, N]``."""
+         out=None, workspace=None, tuning=None):
+    """Decode GEMV, ``x`` fp16 ``[M<=8, K]`` -> fp16 ``[M, N]``.  ``tuning = (slices_per_sm, ctas_per_sm)`` selects
+    ``b200gptq_gemv_tuned`` (see the header for the two parameters); ``None`` means the library defaults."""
     return _matmul("b200gptq_gemv", _lib.OP_GEMV, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits,
-                   group_size, out, workspace)
+                   group_size, out, workspace, tuning)
 
 
 def gemm(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None,
@@ -152,7 +160,7 @@ def gemm(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=Non
 
 
 def gemv_tp(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, exchange, bias=None, x_perm=None,
-            out=None, workspace=None):
+            out=None, workspace=None, tuning=None):
     """Row-parallel decode GEMV with the sum over ranks fused in (``b200gptq_gemv_tp``): ``x`` is this rank's slice of
     the input ``[M<=8, K_local]``, the packed buffers are this rank's shard, ``bias`` is the full bias (the same on
     every rank).  ``exchange`` is a :class:`exchange.PeerExchange`.  Returns the complete result on every rank."""
@@ -176,7 +184,8 @@ def gemv_tp(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, excha
         st = _lib.lib.b200gptq_gemv_tp(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), _ptr(x_perm),
                                        _ptr(bias), _ptr(out), M, K, N, bits, group_size, _ptr(workspace),
                                        workspace.numel() * workspace.element_size(), exchange.rank, exchange.world,
-                                       exchange.peer_table, exchange.timeout_cycles, _stream(dev))
+                                       exchange.peer_table, exchange.timeout_cycles,
+                                       int(tuning[0]) if tuning else 0, int(tuning[1]) if tuning else 0, _stream(dev))
     _lib.check(st, "b200gptq_gemv_tp")
     return out
 

@@ -86,6 +86,8 @@ class QuantLinear(nn.Module):
         # the sum.
         self.exchange = None
         self.tp_bias = None
+        # (slices_per_sm, ctas_per_sm) of b200gptq_gemv_tuned, or None for the library defaults
+        self.gemv_tuning = None
 
     # ---- offline packing (CPU) ----------------------------------------------------------
     def pack(self, linear, scales, zeros, g_idx=None):
@@ -176,7 +178,7 @@ class QuantLinear(nn.Module):
         kw = dict(bias=self.bias, x_perm=self._x_perm)
         args = (self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize)
         if M <= GEMV_MAX_M:
-            y = ops.gemv(x2, *args, **kw)
+            y = ops.gemv(x2, *args, tuning=self.gemv_tuning, **kw)
         elif self._gemm_ok:
             # measured on B200: from 9 rows on, one tensor-core pass (35-45 us for a 4096 x 12288 layer) beats two
             # or more GEMV passes
@@ -202,7 +204,7 @@ class QuantLinear(nn.Module):
             x2 = x2.contiguous()
         if x2.shape[0] <= GEMV_MAX_M:
             y = ops.gemv_tp(x2, self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize,
-                            self.exchange, bias=self.tp_bias, x_perm=self._x_perm)
+                            self.exchange, bias=self.tp_bias, x_perm=self._x_perm, tuning=self.gemv_tuning)
         else:
             import torch.distributed as dist
             saved, self.bias = self.bias, None

@@ -4,17 +4,22 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
 
 Default workload: the 3-bit act-order decode GEMV (K=4096, N=11008, group 128,
-M=1).  One *step* is one pass over a pool of distinct layers of that shape whose
-packed weights together exceed the L2 cache, so every launch streams its weights
-from HBM.  The headline `value` is weight bytes per second over the whole job with
-all inputs resident on the device; `e2e` is the same quantity through
-`QuantLinear.forward` with the activations starting in pinned host memory and the
-results ending there.  Under torchrun every rank runs its own pool (the layers of
-a column-parallel linear are independent: no collective on the data path) and
-rank 0 reports the sum.
+M=1).  One *step* is `passes_per_step` passes over a pool of distinct layers of that
+shape whose packed weights together exceed the L2 cache, so every launch streams its
+weights from HBM; the number of passes is chosen so that the timed region lasts at
+least half a second (sustained clocks, enough clock samples).  The headline `value`
+is weight bytes per second over the whole job with all inputs resident on the device;
+`e2e` is the same quantity through `QuantLinear.forward` with the activations starting
+in pinned host memory and the results ending there.  Under torchrun every rank runs
+its own pool (the layers of a column-parallel linear are independent: no collective
+on the data path) and rank 0 reports the sum; the tensor-parallel models
+(`llama7b_decode`, `opt66b_decode`) ride on the same line, with a check that the
+sharded model computes what the unsharded one computes (`tp_parity`).
 
-`--impl reference` times the reference's CPU dequantise-then-matmul path (the
-oracle port of auto_gptq/nn_modules/qlinear.py:197-243) on the host cores.
+`--impl reference` times the reference's CPU dequantise-then-matmul path
+(auto_gptq/nn_modules/qlinear.py:197-243: the reference's own file when it has been
+staged under oracle/_ref, else the oracle's restatement of it) on the host cores; it
+does not load the CUDA library.
 """
 from __future__ import annotations
 
@@ -42,6 +47,7 @@ POOL_BYTES = 320 << 20  # > 2x the 126 MB L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under profiles/
 NCU_DRAM_BYTES_PER_LAUNCH = {"gemv_b3_k4096_n11008_act": 17805568, "gemv_b4_k4096_n4096": None}
 METRIC = "gemv_weight_GBps"
+MIN_TIMED_MS = 500.0   # the timed region of the headline lasts at least this long
 
 
 def measured_peaks():
@@ -114,29 +120,51 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_baseline(cfg, budget_s=20.0, max_calls=9):
-    """Time the oracle's torch forward (the reference's CPU path) on one layer of the workload."""
-    from autogptq.tvm_b200 import synth
-    from oracle.gptq_oracle import TorchQuantLinearOracle
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
+def reference_forward(cfg):
+    """``(forward, x, layer, kind)``: the reference's CPU forward of one layer of the workload.  ``kind`` is
+    "reference" when the reference's own qlinear.py has been staged under oracle/_ref (oracle/stage_ref.py), else
+    "port" (the oracle's restatement, proven bit-identical to it by tests/test_oracle.py)."""
+    import contextlib
+    import io
+    from autogptq.tvm_b200 import synth          # synthetic tensors only: does not load the CUDA library
+    from oracle import stage_ref
     layer = synth.make_layer(cfg["bits"], cfg["K"], cfg["N"], cfg["group_size"], cfg["act_order"], seed=1)
     x = synth.make_x(cfg["M"], cfg["K"], seed=1)
+    ref = None
+    with contextlib.redirect_stdout(io.StringIO()):
+        ref = stage_ref.load()
+    if ref is not None:
+        mod = ref.QuantLinear(cfg["bits"], cfg["group_size"], cfg["K"], cfg["N"], False)
+        mod.qweight, mod.qzeros, mod.scales, mod.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
+
+        def forward():
+            with contextlib.redirect_stdout(io.StringIO()):   # the reference prints on every call
+                return mod.forward(x)
+        return forward, x, layer, "reference"
+    from oracle.gptq_oracle import TorchQuantLinearOracle
     orc = TorchQuantLinearOracle(cfg["bits"], layer.qweight, layer.qzeros, layer.scales, layer.g_idx)
-    orc.forward(x)  # warm-up
+    return (lambda: orc.forward(x)), x, layer, "port"
+
+
+def cpu_baseline(cfg, budget_s=20.0, max_calls=9):
+    """Time the reference's CPU path on one layer of the workload."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    forward, x, layer, kind = reference_forward(cfg)
+    forward()  # warm-up
     times = []
     t_start = time.perf_counter()
     while len(times) < 3 or (time.perf_counter() - t_start < budget_s and len(times) < max_calls):
         t0 = time.perf_counter()
-        orc.forward(x)
+        forward()
         times.append(time.perf_counter() - t0)
     med = statistics.median(times)
-    return {"value": layer.weight_bytes() / med / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+    return {"value": layer.weight_bytes() / med / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
             "seconds_per_call": med,
             "sample": f"{len(times)} forward calls of one layer of the workload (median), torch CPU, {cores} threads"}
 
 
-def time_gemv_workload(name, dev, steps=30):
+def time_gemv_workload(name, dev, steps=300):
     """Weight GB/s and roofline fraction of another GEMV workload (same method as the headline)."""
     from autogptq.tvm_b200 import QuantLinear, ops, synth, _lib
     cfg = WORKLOADS[name]
@@ -231,7 +259,9 @@ def time_opt66b_decode(dev, world):
 
 def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
     from autogptq.tvm_b200 import decoder
-    m = decoder.GPTQDecoder(cfg, batch=batch, device=dev)
+    # world > 1: the row-parallel linears and the token pick exchange through peer memory inside the library's
+    # kernels (up to 8 rows; larger batches use the process group's all-reduce)
+    m = decoder.GPTQDecoder(cfg, batch=batch, device=dev, fused_allreduce=world > 1)
     prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(11)).to(dev)
     m.prefill(prompt)            # warm-up (builds run-time views, sizes scratch)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -243,6 +273,9 @@ def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
     prefill_ms = e0.elapsed_time(e1)
     m.capture()
     torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
     e0.record()
     toks = m.decode(decode_steps)
     e1.record()
@@ -255,39 +288,49 @@ def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
     ms, prefill_ms = float(t[0]), float(t[1])
     peak, _ = measured_peaks()
     per_tok_s = ms * 1e-3 / decode_steps
-    return {"workload": name, "tp": world, "batch": batch, "decode_tok_s": batch * decode_steps / (ms * 1e-3),
-            "ms_per_token": ms / decode_steps, "prefill_ms": prefill_ms,
-            "weight_bytes_per_token_per_gpu": m.bytes_per_token(),
-            "frac_of_hbm_roofline": m.bytes_per_token() / per_tok_s / 1e9 / peak,
-            "last_token": int(toks[-1, 0])}
+    out = {"workload": name, "tp": world, "batch": batch, "decode_tok_s": batch * decode_steps / (ms * 1e-3),
+           "ms_per_token": ms / decode_steps, "prefill_ms": prefill_ms,
+           "weight_bytes_per_token_per_gpu": m.bytes_per_token(),
+           "frac_of_hbm_roofline": m.bytes_per_token() / per_tok_s / 1e9 / peak,
+           "last_token": int(toks[-1, 0]),
+           "allreduce": "none" if world == 1 else ("fused peer-memory exchange" if batch <= 8 else "process group")}
+    if m.exchange is not None:
+        out["exchange_status"] = m.exchange.status()     # 0: no wait of the fused all-reduce ever ran out
+    return out
+
+
+def tp_parity_llama(dev):
+    """World > 1: the tensor-parallel Llama-7B-architecture model against the same model on rank 0 alone (logits of
+    the prompt's last token and of the first decode step; tolerance of the output contract at the vocabulary
+    projection)."""
+    from autogptq.tvm_b200 import decoder
+    prompt = torch.randint(0, decoder.LLAMA_7B.vocab, (1, 64), generator=torch.Generator().manual_seed(12)).to(dev)
+    return decoder.tp_parity(decoder.LLAMA_7B, prompt, dev, fused_allreduce=True)
 
 
 def run_reference(args, cfg, rank):
     if rank != 0:
         return
-    from autogptq.tvm_b200 import synth
-    from oracle.gptq_oracle import TorchQuantLinearOracle
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    layer = synth.make_layer(cfg["bits"], cfg["K"], cfg["N"], cfg["group_size"], cfg["act_order"], seed=1)
-    x = synth.make_x(cfg["M"], cfg["K"], seed=1)
-    orc = TorchQuantLinearOracle(cfg["bits"], layer.qweight, layer.qzeros, layer.scales, layer.g_idx)
-    steps = min(args.steps, 20)
-    for _ in range(min(args.warmup, 3)):
-        orc.forward(x)
+    forward, x, layer, kind = reference_forward(cfg)
+    steps, warmup = args.steps, max(args.warmup, 3)     # the same counts as the GPU arm
+    for _ in range(warmup):
+        forward()
     t0 = time.perf_counter()
     for _ in range(steps):
-        orc.forward(x)
+        forward()
     dt = (time.perf_counter() - t0) / steps
     val = layer.weight_bytes() / dt / 1e9
     sample = f"each step = one forward of one layer of the workload on the host, {cores} torch threads"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 3), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": args.workload, **cfg},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cuda_library_loaded": "autogptq.tvm_b200._lib" in sys.modules,
     }))
 
 
@@ -300,11 +343,12 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip config 0, the GEMM sweep and the decode run")
-    ap.add_argument("--opt66b", action="store_true",
-                    help="add the OPT-66B-architecture decode runs (config 4) at tensor-parallel degree --gpus")
+    ap.add_argument("--no-opt66b", action="store_true",
+                    help="skip the OPT-66B-architecture decode runs (config 4)")
     ap.add_argument("--gemm-demo", type=int, default=0, metavar="M",
                     help="only launch the config-2 GEMM a few times with M rows (a small target for ncu) and exit")
     args = ap.parse_args()
+    t_program = time.perf_counter()
     cfg = dict(WORKLOADS[args.workload])
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -371,18 +415,34 @@ def main():
         if world > 1:
             dist.barrier()
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    t_load = time.perf_counter()      # the GPU runs the same load from here (warm-up) to the end of the timed steps
-    for _ in range(args.warmup):
-        graph.replay()
-    torch.cuda.synchronize()
-    barrier()
+    # passes per step: enough graph replays that the timed region lasts at least half a second
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        graph.replay()
     torch.cuda.synchronize()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(10):
         graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / 10], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    passes = max(1, int(-(-MIN_TIMED_MS // (float(t[0]) * args.steps))))
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(args.warmup):
+        for _ in range(passes):
+            graph.replay()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    t_load = time.perf_counter()      # clock samples are taken between here and the end of the timed steps
+    e0.record()
+    for _ in range(args.steps):
+        for _ in range(passes):
+            graph.replay()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
@@ -425,26 +485,34 @@ def main():
         torch.cuda.empty_cache()
         barrier()
         extras["llama7b_decode"] = time_llama_decode(dev, world)   # every rank takes part (tensor parallel)
-    if args.opt66b:
-        torch.cuda.empty_cache()
-        barrier()
-        extras["opt66b_decode"] = time_opt66b_decode(dev, world)
+        if world > 1:
+            torch.cuda.empty_cache()
+            barrier()
+            par = tp_parity_llama(dev)
+            if rank == 0:
+                extras["llama7b_decode"]["tp_parity"] = par
+        # config 4 rides on the same line; on one GPU only while the run is still within its time budget
+        if not args.no_opt66b and (world > 1 or time.perf_counter() - t_program < 300.0):
+            torch.cuda.empty_cache()
+            barrier()
+            extras["opt66b_decode"] = time_opt66b_decode(dev, world)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
         ms_per_step = ms / args.steps
         wbytes = proto.weight_bytes()
         abytes = proto.algorithmic_bytes(M)
-        launch_s = ms_per_step * 1e-3 / P
-        value = world * P * wbytes / (ms_per_step * 1e-3) / 1e9
+        launch_s = ms_per_step * 1e-3 / (P * passes)
+        value = world * P * passes * wbytes / (ms_per_step * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, **cfg, "pool_layers": P,
-                       "l2_policy": f"each step streams {P} distinct layers ({P * wbytes >> 20} MiB of weights) > L2",
+            "config": {"workload": args.workload, **cfg, "pool_layers": P, "passes_per_step": passes,
+                       "l2_policy": f"every pass streams {P} distinct layers ({P * wbytes >> 20} MiB of weights) > L2",
                        "act_order_handling": "rows sorted by group once at load; x gathered in-kernel",
-                       "launch": "one CUDA graph replay per step"},
+                       "launch": "one CUDA graph replay per pass, one layer per kernel launch",
+                       "timed_region_ms": ms},
             "roofline": {"bound": "hbm", "achieved": abytes / launch_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": abytes / launch_s / 1e9 / peak, "traffic": None,
                          "peak_kind": peak_kind, "us_per_launch": launch_s * 1e6,
@@ -453,10 +521,12 @@ def main():
             "e2e": {"value": world * P * wbytes / e2e_s / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": P * M * K * 2, "d2h_bytes_per_step": P * M * N * 2,
                     "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
-            "gpu_launches": args.steps * P + e2e_steps * P + sum(v.get("launches", 0) for v in extras.values() if isinstance(v, dict)),
+            "gpu_launches": args.steps * P * passes + e2e_steps * P + sum(v.get("launches", 0) for v in extras.values() if isinstance(v, dict)),
             "clocks": clocks,
         }
         line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
+        # sticky status word of the kernels' bounded waits (last word of the counter region): 0 = none ran out
+        line["bounded_waits_expired"] = bool(int(ws[16380:16384].view(torch.int32)[0]) != 0)
         line.update(extras)
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cfg)

@@ -105,6 +105,25 @@ B200GPTQ_API int b200gptq_gemv(const void* x, const int32_t* qweight, const int3
                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * b200gptq_gemv with the two tuning parameters of the streaming kernel made explicit (0 = the library's
+ * default for that parameter; other kernels ignore them).  The reference tunes its kernels per shape and
+ * per row bucket (tile tables of pycuda_warpper.py:77-127, NNI search results in .cache/handler_database.json);
+ * here the kernel is one and what remains to tune is how it shares the GPU with its neighbours in the stream:
+ *   slices_per_sm  the K range of a 256-column group is cut into as many slices (CTAs) as give the grid about
+ *                  this many CTAs per SM (at most 8 slices).  Default 3 for one row of x, 2 otherwise.
+ *   ctas_per_sm    shared-memory footprint: a CTA takes at most 1/ctas_per_sm of an SM, so that many CTAs -- of
+ *                  this launch and of its neighbours -- can be resident together; a slice that does not fit is
+ *                  streamed through a ring.  Default: 3 if the whole slice still fits, else 2.
+ * Measured on B200: a chain of nothing but GEMVs (the benchmark's pool of layers) is fastest with the defaults;
+ * a decode step, where small kernels sit between the GEMVs, is fastest with (2, 3).
+ */
+B200GPTQ_API int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                        const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
+                        int M, int K, int N, int bits, int group_size,
+                        void* workspace, size_t workspace_bytes,
+                        int slices_per_sm, int ctas_per_sm, void* stream);
+
+/*
  * Which kernel b200gptq_gemv runs for this problem: B200GPTQ_PATH_STREAM or
  * B200GPTQ_PATH_GENERIC (a negative B200GPTQ_ERR_* code for an invalid problem).
  * Host-only; launches nothing.  has_g_idx != 0 means a non-NULL g_idx is passed.
@@ -206,11 +225,11 @@ B200GPTQ_API size_t b200gptq_gemv_static_capacity(void);
  * same M and N.  Limits: world <= 8, M <= 8, N <= 16384.
  *
  * Waits are bounded: a rank that does not see a peer's counter within `timeout_cycles` GPU clock
- * cycles (<= 0: 2e9) raises the sticky status word at byte 0 of its own buffer to 2, finishes with
+ * cycles (<= 0: 2e10, about ten seconds) raises the sticky status word at byte 0 of its own buffer to 2, finishes with
  * undefined results and returns control; b200gptq_tp_status() reads the word (it synchronises the
  * stream).  Counters only grow, so the calls can be captured in a CUDA graph and replayed.
  *
- *   b200gptq_gemv_tp       y = sum over ranks of (x_r @ W_r) + bias; same arguments as b200gptq_gemv
+ *   b200gptq_gemv_tp       y = sum over ranks of (x_r @ W_r) + bias; same arguments as b200gptq_gemv_tuned
  *                          for this rank's shard.  `bias` (full, the same on every rank) is added
  *                          after the sum.  With g_idx == NULL the exchange runs inside the GEMV
  *                          kernel's combine step; shards that need the general kernel (act-order
@@ -223,7 +242,8 @@ B200GPTQ_API int b200gptq_gemv_tp(const void* x, const int32_t* qweight, const i
                      const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
                      int M, int K, int N, int bits, int group_size,
                      void* workspace, size_t workspace_bytes,
-                     int rank, int world, void* const* peer_buffers, long long timeout_cycles, void* stream);
+                     int rank, int world, void* const* peer_buffers, long long timeout_cycles,
+                     int slices_per_sm, int ctas_per_sm, void* stream);
 B200GPTQ_API int b200gptq_tp_allreduce(void* y, const void* bias, int M, int N, int rank, int world,
                           void* const* peer_buffers, long long timeout_cycles, void* stream);
 B200GPTQ_API int b200gptq_tp_status(const void* own_buffer, void* stream, unsigned int* host_out);

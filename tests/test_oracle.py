@@ -98,16 +98,17 @@ def test_zero_point_plus_one_is_not_masked():
     assert z3.shape == (1, 32) and np.all(z3 == 8)
 
 
-REF_ROOT = os.environ.get("GPTQ_REFERENCE_ROOT", "/root/reference")
+# The live reference: a checkout named by the environment, else the file staged by oracle/stage_ref.py.
+REF_ROOT = os.environ.get("B200GPTQ_REFERENCE", os.environ.get("GPTQ_REFERENCE_ROOT", ""))
+_STAGED = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "qlinear.py")
+REF_FILE = os.path.join(REF_ROOT, "auto_gptq/nn_modules/qlinear.py") if REF_ROOT else _STAGED
 
 
-@pytest.mark.skipif(not os.path.isfile(os.path.join(REF_ROOT, "auto_gptq/nn_modules/qlinear.py")),
-                    reason="reference checkout not present on this machine")
+@pytest.mark.skipif(not os.path.isfile(REF_FILE), reason="no reference checkout named and nothing staged")
 @pytest.mark.parametrize("bits,K,N,gs,act", [(4, 1024, 256, 128, False), (3, 1024, 256, 128, True),
                                              (4, 512, 128, 32, True), (3, 512, 96, -1, False)])
 def test_oracle_equals_live_reference(bits, K, N, gs, act):
-    spec = importlib.util.spec_from_file_location(
-        "_ref_qlinear", os.path.join(REF_ROOT, "auto_gptq/nn_modules/qlinear.py"))
+    spec = importlib.util.spec_from_file_location("_ref_qlinear", REF_FILE)
     ref = importlib.util.module_from_spec(spec)
     with contextlib.redirect_stdout(io.StringIO()):
         spec.loader.exec_module(ref)
