@@ -1,5 +1,6 @@
 // extern "C" boundary: argument validation and dispatch.  See include/b200gptq.h.
 #include <mutex>
+#include <new>
 
 #include "common.cuh"
 
@@ -40,6 +41,12 @@ int gemv_stream_dispatch_knobs(const __half*, const int32_t*, const int32_t*, co
 size_t gemm_workspace_bytes(int M, int K, int N, int bits);
 int gemm_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*, const int32_t*,
                   const __half*, __half*, int, int, int, int, int, void*, size_t, cudaStream_t);
+
+struct GemvStreamPlan;
+GemvStreamPlan* gemv_stream_plan_create(const int32_t*, const __half*, bool, int, int, int, int, int, const int*, int*);
+int gemv_stream_plan_run(const GemvStreamPlan*, const __half*, const int32_t*, const int32_t*, const __half*, __half*,
+                         void*, cudaStream_t);
+void gemv_stream_plan_destroy(GemvStreamPlan*);
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -157,6 +164,60 @@ int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, const int32_t* qz
     return gemv_generic_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
                                  g_idx, x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K, N,
                                  bits, group_size, workspace, st);
+}
+
+// A plan remembers the layer and everything that can be decided before x is known.
+struct b200gptq_gemv_plan {
+    const int32_t *qweight, *qzeros, *g_idx, *x_perm;
+    const __half *scales, *bias;
+    int M, K, N, bits, group_size, slices_per_sm, ctas_per_sm;
+    size_t workspace_need;
+    b200gptq::GemvStreamPlan* stream;   // NULL: the general kernel serves this problem
+};
+
+int b200gptq_gemv_plan_create(b200gptq_gemv_plan** out, const int32_t* qweight, const int32_t* qzeros,
+                              const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,
+                              int M, int K, int N, int bits, int group_size, int slices_per_sm, int ctas_per_sm) {
+    if (!out || !qweight || !qzeros || !scales) return B200GPTQ_ERR_NULL_POINTER;
+    *out = nullptr;
+    if (int st = check_layer(K, N, bits, &group_size)) return st;
+    if (M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
+    if (slices_per_sm < 0 || slices_per_sm > 8 || ctas_per_sm < 0 || ctas_per_sm > 4) return B200GPTQ_ERR_SHAPE;
+    if (!aligned16(qweight) || !aligned16(scales) || !aligned16(qzeros)) return B200GPTQ_ERR_ALIGNMENT;
+    b200gptq_gemv_plan* p = new (std::nothrow) b200gptq_gemv_plan;
+    if (!p) return B200GPTQ_ERR_CUDA;
+    *p = {qweight, qzeros, g_idx, x_perm, static_cast<const __half*>(scales), static_cast<const __half*>(bias),
+          M, K, N, bits, group_size, slices_per_sm, ctas_per_sm,
+          b200gptq_workspace_bytes(B200GPTQ_OP_GEMV, M, K, N, bits), nullptr};
+    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size)) {
+        const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
+        int st = B200GPTQ_OK;
+        p->stream = gemv_stream_plan_create(qweight, p->scales, x_perm != nullptr, M, K, N, bits, group_size,
+                                            (slices_per_sm || ctas_per_sm) ? knobs : nullptr, &st);
+        if (!p->stream) { delete p; return st; }
+    }
+    *out = p;
+    return B200GPTQ_OK;
+}
+
+int b200gptq_gemv_plan_run(const b200gptq_gemv_plan* p, const void* x, void* y, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+    if (!p || !x || !y) return B200GPTQ_ERR_NULL_POINTER;
+    if (!aligned16(x) || !aligned16(y) || (workspace && !aligned16(workspace))) return B200GPTQ_ERR_ALIGNMENT;
+    if (!workspace || workspace_bytes < p->workspace_need) return B200GPTQ_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (p->stream)
+        return gemv_stream_plan_run(p->stream, static_cast<const __half*>(x), p->qzeros, p->x_perm, p->bias,
+                                    static_cast<__half*>(y), workspace, st);
+    return gemv_generic_dispatch(static_cast<const __half*>(x), p->qweight, p->qzeros, p->scales, p->g_idx, p->x_perm,
+                                 p->bias, static_cast<__half*>(y), p->M, p->K, p->N, p->bits, p->group_size, workspace,
+                                 st);
+}
+
+void b200gptq_gemv_plan_destroy(b200gptq_gemv_plan* p) {
+    if (!p) return;
+    if (p->stream) gemv_stream_plan_destroy(p->stream);
+    delete p;
 }
 
 int b200gptq_gemm(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,

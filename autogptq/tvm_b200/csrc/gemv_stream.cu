@@ -47,6 +47,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <new>
 
 #include "common.cuh"
 #include "tp_exchange.cuh"
@@ -819,25 +820,30 @@ int set_smem_attr_once() {
     return B200GPTQ_OK;
 }
 
-template <int BITS>
-int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
-                  const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int group_size,
-                  void* workspace, cudaStream_t stream, const int* knobs, const TpArgs* tp_args) {
-    int smem_bytes = 0;
-    const Plan plan = make_plan<BITS>(M, K, N, group_size, x_perm != nullptr, knobs, &smem_bytes);
-    unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
-    if (int st = set_smem_attr_once<BITS>()) return st;
+// Everything about a launch that does not change from call to call: the plan, the two tensor maps (which name
+// the layer's qweight and scales) and the kernel instantiation.
+struct PreparedStream {
+    Plan plan;
+    int smem_bytes;
+    int M, K, N, group_size;
+    CUtensorMap tmap_w, tmap_s;
+    const void* kernel;
+};
 
+template <int BITS>
+int prepare_stream(PreparedStream* ps, const int32_t* qweight, const __half* scales, bool has_perm, int M, int K, int N,
+                   int group_size, const int* knobs) {
+    ps->plan = make_plan<BITS>(M, K, N, group_size, has_perm, knobs, &ps->smem_bytes);
+    ps->M = M; ps->K = K; ps->N = N; ps->group_size = group_size;
     const EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) { set_last_cuda_error((int)cudaErrorNotSupported); return B200GPTQ_ERR_CUDA; }
-    CUtensorMap tmap_w, tmap_s;
     {
         // qweight [K/32*bits, N] as a 3-D tensor {32 columns, word-rows, N/32 column chunks}; a box is one unit
         const cuuint64_t dims[3] = {32, (cuuint64_t)(K / 32 * BITS), (cuuint64_t)(N / 32)};
         const cuuint64_t strides[2] = {(cuuint64_t)N * sizeof(int32_t), 32 * sizeof(int32_t)};
         const cuuint32_t box[3] = {32, (cuuint32_t)Traits<BITS>::kWordRows, (cuuint32_t)(kCgCols / 32)};
         const cuuint32_t estr[3] = {1, 1, 1};
-        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(qweight), dims,
+        const CUresult r = encode(&ps->tmap_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(qweight), dims,
                                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
@@ -847,37 +853,59 @@ int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros
         const int G = (K + group_size - 1) / group_size;
         const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)G};
         const cuuint64_t strides[1] = {(cuuint64_t)N * sizeof(__half)};
-        const cuuint32_t box[2] = {(cuuint32_t)kCgCols, (cuuint32_t)plan.group_box};
+        const cuuint32_t box[2] = {(cuuint32_t)kCgCols, (cuuint32_t)ps->plan.group_box};
         const cuuint32_t estr[2] = {1, 1};
-        const CUresult r = encode(&tmap_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(scales), dims,
+        const CUresult r = encode(&ps->tmap_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(scales), dims,
                                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
     }
+    ps->kernel = M == 1 ? (has_perm ? (const void*)gemv_stream_kernel<BITS, false, true>
+                                    : (const void*)gemv_stream_kernel<BITS, false, false>)
+                        : (has_perm ? (const void*)gemv_stream_kernel<BITS, true, true>
+                                    : (const void*)gemv_stream_kernel<BITS, true, false>);
+    return B200GPTQ_OK;
+}
+
+template <int BITS>
+int launch_prepared(const PreparedStream& ps, const __half* x, const int32_t* qzeros, const int32_t* x_perm,
+                    const __half* bias, __half* y, void* workspace, cudaStream_t stream, const TpArgs* tp_args) {
+    unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
+    if (int st = set_smem_attr_once<BITS>()) return st;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(plan.cgs * plan.cluster);
+    cfg.gridDim = dim3(ps.plan.cgs * ps.plan.cluster);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.dynamicSmemBytes = ps.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = plan.cluster;
+    attr[0].val.clusterDim.x = ps.plan.cluster;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    auto kernel = M == 1 ? (x_perm ? gemv_stream_kernel<BITS, false, true> : gemv_stream_kernel<BITS, false, false>)
-                         : (x_perm ? gemv_stream_kernel<BITS, true, true> : gemv_stream_kernel<BITS, true, false>);
     TpArgs tp = {};
     if (tp_args) {
-        if (plan.cgs > kTpMaxGroups) return B200GPTQ_ERR_TOO_LARGE;
+        if (ps.plan.cgs > kTpMaxGroups) return B200GPTQ_ERR_TOO_LARGE;
         tp = *tp_args;
     }
-    B200GPTQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmap_w, tmap_s, x, qzeros, x_perm, bias, y, M, K, N,
-                                         group_size, plan, status, tp));
+    int M = ps.M, K = ps.K, N = ps.N, group_size = ps.group_size;
+    Plan plan = ps.plan;
+    void* args[] = {const_cast<CUtensorMap*>(&ps.tmap_w), const_cast<CUtensorMap*>(&ps.tmap_s), &x, &qzeros, &x_perm,
+                    &bias, &y, &M, &K, &N, &group_size, &plan, &status, &tp};
+    B200GPTQ_CUDA_TRY(cudaLaunchKernelExC(&cfg, ps.kernel, args));
     return B200GPTQ_OK;
+}
+
+template <int BITS>
+int launch_stream(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
+                  const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N, int group_size,
+                  void* workspace, cudaStream_t stream, const int* knobs, const TpArgs* tp_args) {
+    PreparedStream ps;
+    if (int st = prepare_stream<BITS>(&ps, qweight, scales, x_perm != nullptr, M, K, N, group_size, knobs)) return st;
+    return launch_prepared<BITS>(ps, x, qzeros, x_perm, bias, y, workspace, stream, tp_args);
 }
 
 }  // namespace
@@ -915,6 +943,31 @@ int gemv_stream_dispatch_knobs(const __half* x, const int32_t* qweight, const in
     return gemv_stream_dispatch_tp(x, qweight, qzeros, scales, x_perm, bias, y, M, K, N, bits, group_size, workspace,
                                    stream, knobs, nullptr);
 }
+
+// A prepared launch as an opaque object (b200gptq_gemv_plan_*): built once per (layer, row count), run many times.
+struct GemvStreamPlan {
+    int bits;
+    PreparedStream ps;
+};
+
+GemvStreamPlan* gemv_stream_plan_create(const int32_t* qweight, const __half* scales, bool has_perm, int M, int K, int N,
+                                        int bits, int group_size, const int* knobs, int* status_out) {
+    GemvStreamPlan* p = new (std::nothrow) GemvStreamPlan;
+    if (!p) { *status_out = B200GPTQ_ERR_CUDA; return nullptr; }
+    p->bits = bits;
+    *status_out = bits == 4 ? prepare_stream<4>(&p->ps, qweight, scales, has_perm, M, K, N, group_size, knobs)
+                            : prepare_stream<3>(&p->ps, qweight, scales, has_perm, M, K, N, group_size, knobs);
+    if (*status_out != B200GPTQ_OK) { delete p; return nullptr; }
+    return p;
+}
+
+int gemv_stream_plan_run(const GemvStreamPlan* p, const __half* x, const int32_t* qzeros, const int32_t* x_perm,
+                         const __half* bias, __half* y, void* workspace, cudaStream_t stream) {
+    return p->bits == 4 ? launch_prepared<4>(p->ps, x, qzeros, x_perm, bias, y, workspace, stream, nullptr)
+                        : launch_prepared<3>(p->ps, x, qzeros, x_perm, bias, y, workspace, stream, nullptr);
+}
+
+void gemv_stream_plan_destroy(GemvStreamPlan* p) { delete p; }
 
 int gemv_stream_dispatch(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                          const int32_t* g_idx, const int32_t* x_perm, const __half* bias, __half* y, int M, int K,

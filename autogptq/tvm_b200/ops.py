@@ -159,6 +159,49 @@ def gemm(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=Non
                    group_size, out, workspace)
 
 
+class GemvPlan:
+    """A prepared decode GEMV for one layer and one row count (``b200gptq_gemv_plan_*``): kernel choice, work split
+    and TMA descriptors are built once, a call is one kernel launch.  Keeps the layer's tensors alive."""
+
+    def __init__(self, qweight, qzeros, scales, g_idx, x_perm, bias, M: int, bits: int, group_size: int, tuning=None):
+        _need_cuda("qweight", qweight, torch.int32)
+        _need_cuda("qzeros", qzeros, torch.int32)
+        _need_cuda("scales", scales, torch.float16)
+        for name, t, dt in (("g_idx", g_idx, torch.int32), ("x_perm", x_perm, torch.int32), ("bias", bias, torch.float16)):
+            if t is not None:
+                _need_cuda(name, t, dt)
+        self._keep = (qweight, qzeros, scales, g_idx, x_perm, bias)
+        self.M = M
+        self.K, self.N = layer_dims(qweight, bits)
+        self.device = qweight.device
+        import ctypes
+        handle = ctypes.c_void_p(0)
+        st = _lib.lib.b200gptq_gemv_plan_create(ctypes.byref(handle), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
+                                                _ptr(x_perm), _ptr(bias), M, self.K, self.N, bits, group_size,
+                                                int(tuning[0]) if tuning else 0, int(tuning[1]) if tuning else 0)
+        _lib.check(st, "b200gptq_gemv_plan_create")
+        self._handle = handle
+        self._need = _lib.workspace_bytes(_lib.OP_GEMV, M, self.K, self.N, bits)
+        self._ws = get_workspace(self.device, self._need)
+        self._ws_ptr, self._ws_bytes = self._ws.data_ptr(), self._ws.numel()
+
+    def run(self, x, out=None):
+        if not x.is_cuda or x.dtype != torch.float16 or not x.is_contiguous() or tuple(x.shape) != (self.M, self.K):
+            raise ValueError(f"x must be a contiguous fp16 CUDA tensor [{self.M}, {self.K}]")
+        if out is None:
+            out = torch.empty((self.M, self.N), dtype=torch.float16, device=x.device)
+        st = _lib.lib.b200gptq_gemv_plan_run(self._handle, x.data_ptr(), out.data_ptr(), self._ws_ptr, self._ws_bytes,
+                                             torch.cuda.current_stream(x.device).cuda_stream)
+        if st:
+            _lib.check(st, "b200gptq_gemv_plan_run")
+        return out
+
+    def __del__(self):
+        h, self._handle = getattr(self, "_handle", None), None
+        if h:
+            _lib.lib.b200gptq_gemv_plan_destroy(h)
+
+
 def gemv_tp(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, exchange, bias=None, x_perm=None,
             out=None, workspace=None, tuning=None):
     """Row-parallel decode GEMV with the sum over ranks fused in (``b200gptq_gemv_tp``): ``x`` is this rank's slice of

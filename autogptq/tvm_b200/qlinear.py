@@ -88,6 +88,7 @@ class QuantLinear(nn.Module):
         self.tp_bias = None
         # (slices_per_sm, ctas_per_sm) of b200gptq_gemv_tuned, or None for the library defaults
         self.gemv_tuning = None
+        self._plans = {}           # row count -> ops.GemvPlan (prepared launches of the decode GEMV)
 
     # ---- offline packing (CPU) ----------------------------------------------------------
     def pack(self, linear, scales, zeros, g_idx=None):
@@ -159,6 +160,7 @@ class QuantLinear(nn.Module):
         else:
             b = g_run.view(K // 32, 32)
             self._gemm_ok = self.bits in (3, 4) and bool((b == b[:, :1]).all().item())
+        self._plans = {}
         self._ready_for = (dev, self.qweight.data_ptr(), self.g_idx.data_ptr())
 
     def _ready(self) -> bool:
@@ -178,7 +180,14 @@ class QuantLinear(nn.Module):
         kw = dict(bias=self.bias, x_perm=self._x_perm)
         args = (self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize)
         if M <= GEMV_MAX_M:
-            y = ops.gemv(x2, *args, tuning=self.gemv_tuning, **kw)
+            key = (M, self.gemv_tuning)
+            plan = self._plans.get(key)
+            if plan is None or plan._keep[5] is not self.bias:
+                plan = self._plans[key] = ops.GemvPlan(self._qweight_run, self.qzeros, self.scales, self._g_idx_run,
+                                                     self._x_perm, self.bias, M, self.bits, self.groupsize,
+                                                     self.gemv_tuning)
+            with torch.cuda.device(x2.device):
+                y = plan.run(x2)
         elif self._gemm_ok:
             # measured on B200: from 9 rows on, one tensor-core pass (35-45 us for a 4096 x 12288 layer) beats two
             # or more GEMV passes

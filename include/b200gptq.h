@@ -124,6 +124,23 @@ B200GPTQ_API int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, cons
                         int slices_per_sm, int ctas_per_sm, void* stream);
 
 /*
+ * The same GEMV as a plan: what can be decided before x is known (kernel choice, work split, the TMA
+ * descriptors of the layer's qweight and scales) is built once per (layer, M) and kept in an opaque HOST
+ * object, so that a call costs one kernel launch.  This is the counterpart of the reference's per-shape
+ * handler objects (tvm_untils/cache.py:10-60 keeps them in a module-level dict; here the caller owns the plan
+ * and the library keeps no table).  The plan holds the layer's device pointers, not copies: the buffers must
+ * outlive it and stay where they are.  A plan may be run from several threads and streams at once with
+ * different workspaces.  plan_run has the semantics of b200gptq_gemv_tuned with the arguments given at creation.
+ */
+typedef struct b200gptq_gemv_plan b200gptq_gemv_plan;
+B200GPTQ_API int b200gptq_gemv_plan_create(b200gptq_gemv_plan** out, const int32_t* qweight, const int32_t* qzeros,
+                              const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,
+                              int M, int K, int N, int bits, int group_size, int slices_per_sm, int ctas_per_sm);
+B200GPTQ_API int b200gptq_gemv_plan_run(const b200gptq_gemv_plan* plan, const void* x, void* y,
+                           void* workspace, size_t workspace_bytes, void* stream);
+B200GPTQ_API void b200gptq_gemv_plan_destroy(b200gptq_gemv_plan* plan);
+
+/*
  * Which kernel b200gptq_gemv runs for this problem: B200GPTQ_PATH_STREAM or
  * B200GPTQ_PATH_GENERIC (a negative B200GPTQ_ERR_* code for an invalid problem).
  * Host-only; launches nothing.  has_g_idx != 0 means a non-NULL g_idx is passed.

@@ -39,8 +39,17 @@ def test_rows_decide_the_entry_point(monkeypatch, bits, M, want):
             return out if out is not None else torch.zeros((x.shape[0], 64), dtype=torch.float16)
         return f
 
+    class FakePlan:   # up to 8 rows go through a prepared launch (ops.GemvPlan)
+        def __init__(self, *a, **k):
+            self._keep = (None,) * 6
+
+        def run(self, x, out=None):
+            return fake("gemv")(x, out=out)
+
+    monkeypatch.setattr(ql.ops, "GemvPlan", FakePlan)
     monkeypatch.setattr(ql.ops, "gemv", fake("gemv"))
     monkeypatch.setattr(ql.ops, "gemm", fake("gemm"))
+    monkeypatch.setattr(torch.cuda, "device", lambda d: __import__("contextlib").nullcontext())
     monkeypatch.setattr(torch, "empty", lambda *a, device=None, **k: torch.zeros(*a, **k))
     x = torch.zeros((M, 256), dtype=torch.float16).as_subclass(_FakeCuda)
     y = _layer(bits, groupsize).forward(x)

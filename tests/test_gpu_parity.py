@@ -173,6 +173,26 @@ def test_streaming_gemv_vs_oracle(bits, K, N, gs, bias, M):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("bits,K,N,gs,act,M", [(4, 4096, 4096, 128, False, 1), (3, 2048, 1056, 128, False, 5),
+                                               (4, 512, 96, 64, True, 2), (8, 256, 96, 128, False, 8)])
+def test_prepared_plan_equals_the_stateless_call(bits, K, N, gs, act, M):
+    """b200gptq_gemv_plan_* (one launch per call, descriptors built once) against b200gptq_gemv and
+    b200gptq_gemv_tuned with other tuning parameters: same bits, and the plan can be run repeatedly."""
+    layer = synth.make_layer(bits, K, N, gs, act, bias=True, seed=K + M).to(DEV)
+    g = layer.g_idx if act else None
+    x = synth.make_x(M, K, seed=M, device=DEV)
+    want = ops.gemv(x, layer.qweight, layer.qzeros, layer.scales, g, bits, gs, bias=layer.bias)
+    plan = ops.GemvPlan(layer.qweight, layer.qzeros, layer.scales, g, None, layer.bias, M, bits, gs)
+    for _ in range(3):
+        assert torch.equal(plan.run(x), want)
+    tuned = ops.gemv(x, layer.qweight, layer.qzeros, layer.scales, g, bits, gs, bias=layer.bias, tuning=(2, 3))
+    # a different K split sums in a different order: equal within the tolerance, not necessarily bit for bit
+    _check_output(tuned, x.cpu().numpy(), O.dequantize(*_layer_np(layer.to("cpu")), bits)[2], layer.bias.cpu().numpy())
+    with pytest.raises(ValueError):
+        plan.run(x[:, :K // 2].contiguous())
+    del plan
+
+
 @pytest.mark.parametrize("bits,K,N,gs", [(4, 4096, 4096, 128), (3, 4096, 11008, 128), (4, 1024, 544, 64)])
 @pytest.mark.parametrize("M", [1, 4])
 def test_sorted_rows_path_matches_oracle(bits, K, N, gs, M):
