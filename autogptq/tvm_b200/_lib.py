@@ -38,6 +38,7 @@ _SIGNATURES = {
     "b200gptq_tp_allreduce": (_c_int, [_c_void_p] * 2 + [_c_int] * 4 + [_c_void_p, ctypes.c_longlong, _c_void_p]),
     "b200gptq_tp_status": (_c_int, [_c_void_p, _c_void_p, _c_void_p]),
     "b200gptq_tp_enable_peer": (_c_int, [_c_int]),
+    "b200gptq_tp_export": (_c_int, [_c_void_p, _c_void_p, _c_void_p]),
     "b200gptq_tp_open_peer": (_c_int, [_c_void_p, _c_void_p]),
     "b200gptq_tp_close_peer": (_c_int, [_c_void_p]),
     "b200gptq_tp_probe": (_c_int, [_c_void_p, _c_void_p]),

@@ -1,6 +1,8 @@
 // Tensor-parallel entry points of the C ABI: the row-parallel decode GEMV with its all-reduce fused into
 // the combine step, and the same exchange as a kernel of its own for results that other kernels produced.
 // See tp_exchange.cuh for the protocol and include/b200gptq.h for the contract.
+#include <cuda.h>
+
 #include <cstring>
 
 #include "common.cuh"
@@ -131,6 +133,32 @@ int b200gptq_tp_enable_peer(int peer_device) {
     const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
     if (e == cudaErrorPeerAccessAlreadyEnabled) { (void)cudaGetLastError(); return B200GPTQ_OK; }
     B200GPTQ_CUDA_TRY(e);
+    return B200GPTQ_OK;
+}
+
+int b200gptq_tp_export(const void* device_ptr, void* ipc_handle_out, size_t* offset_out) {
+    if (!device_ptr || !ipc_handle_out || !offset_out) return B200GPTQ_ERR_NULL_POINTER;
+    // the handle names the whole allocation that contains the pointer; the offset locates the pointer inside it
+    typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static const RangeFn range = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<RangeFn>(p);
+    }();
+    if (!range) { set_last_cuda_error((int)cudaErrorNotSupported); return B200GPTQ_ERR_CUDA; }
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (range(&base, &size, (CUdeviceptr)device_ptr) != CUDA_SUCCESS) {
+        set_last_cuda_error((int)cudaErrorInvalidValue);
+        return B200GPTQ_ERR_CUDA;
+    }
+    cudaIpcMemHandle_t h;
+    B200GPTQ_CUDA_TRY(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+    memcpy(ipc_handle_out, &h, sizeof(h));
+    *offset_out = (size_t)((CUdeviceptr)device_ptr - base);
     return B200GPTQ_OK;
 }
 

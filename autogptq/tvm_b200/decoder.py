@@ -103,12 +103,18 @@ class DecoderLayer:
         full = _full_layer(cfg, cfg.hidden, cfg.hidden, bias, seed + 2, device)
         self.o = _to_module(tp.shard_row(full, rank, world, sizes=head_sizes)[0], device)
         self.o.tp_bias = full.bias          # the fused all-reduce adds the whole bias on every rank
-        full = _full_layer(cfg, cfg.hidden, up_parts * cfg.inter, bias, seed + 3, device)
-        self.up = _to_module(tp.shard_column(full, rank, world, parts=up_parts, sizes=inter_sizes), device)
+        full_up = _full_layer(cfg, cfg.hidden, up_parts * cfg.inter, bias, seed + 3, device)
         full = _full_layer(cfg, cfg.inter, cfg.hidden, bias, seed + 4, device)
+        if cfg.desc_act:
+            # The FFN's second linear reads an element-wise function of the first one's output: its act-order row
+            # permutation is folded into the first one's column order once, here, after which it is an ordinary
+            # layer (no gather of its input, whole groups per rank).  The pair computes the same function.
+            qs, perm, _ = ops.sort_rows(full.qweight.contiguous(), full.g_idx.contiguous(), cfg.bits)
+            full, full_up = tp.fold_act_order(full, full_up, qs, perm, parts=up_parts)
+        self.up = _to_module(tp.shard_column(full_up, rank, world, parts=up_parts, sizes=inter_sizes), device)
         self.down = _to_module(tp.shard_row(full, rank, world, sizes=inter_sizes)[0], device)
         self.down.tp_bias = full.bias
-        del full
+        del full, full_up
         g = torch.Generator(device=device).manual_seed(seed + 5)
         self.norm1_w = 1.0 + 0.01 * torch.randn(cfg.hidden, generator=g, device=device, dtype=torch.float16)
         self.norm2_w = 1.0 + 0.01 * torch.randn(cfg.hidden, generator=g, device=device, dtype=torch.float16)
@@ -370,6 +376,17 @@ class GPTQDecoder:
             out[i].copy_(self.tokens)
         return out
 
+    def close(self) -> None:
+        """Release the peer-memory exchange (every rank, after the last step has been synchronised)."""
+        if self.exchange is not None:
+            torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            self.exchange.close()
+            self.exchange = None
+            for L in self.layers:
+                L.o.exchange = L.down.exchange = None
+
     def gather_logits(self) -> torch.Tensor:
         """The latest logits over the whole vocabulary ``[B, vocab]`` (every rank gets them)."""
         lg = self.last_logits
@@ -407,15 +424,17 @@ def tp_parity(cfg: DecoderConfig, prompt: torch.Tensor, device, fused_allreduce:
     m.tokens.copy_(tok)           # both models continue from the same token even if a near-tie picked differently
     m.decode(1)
     lg_step = m.gather_logits()
+    m.close()
     if rank != 0:
         return {}
     ref_prompt = ref.last_logits[:, :cfg.vocab]
     h = ref.last_hidden.float()
     ref.decode(1)
     ref_step = ref.last_logits[:, :cfg.vocab]
+    world = m.world
     wmax = float(ref.lm_head.float().abs().max())
     tol = 1e-2 * float(h.norm(dim=-1).min()) * wmax
     finite = torch.isfinite(ref_prompt) & torch.isfinite(ref_step)
     err = max(float(((lg_prompt - ref_prompt).abs() * finite).max()), float(((lg_step - ref_step).abs() * finite).max()))
-    return {"max_abs_err": err, "tol": tol, "ok": bool(err <= tol), "world": m.world,
+    return {"max_abs_err": err, "tol": tol, "ok": bool(err <= tol), "world": world,
             "fused_allreduce": bool(fused_allreduce), "same_first_token": bool(torch.equal(m.tokens, ref.tokens))}

@@ -34,15 +34,11 @@ class PeerExchange:
         self.own = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)   # zero-filled once
         torch.cuda.synchronize(self.device)
         # the IPC handle names the allocation the buffer was carved from; the buffer starts `offset` bytes into it
-        shared = self.own.untyped_storage()._share_cuda_()
-        handle, offset = bytes(shared[1]), int(shared[3]) + self.own.storage_offset()
-        if len(handle) != 64:
-            # newer torch versions put a version byte and an allocation-kind byte ('c': plain cudaMalloc) in front
-            if len(handle) == 66 and handle[1:2] == b"c":
-                handle = handle[2:]
-            else:
-                raise RuntimeError("the exchange buffer must come from a plain cudaMalloc allocation "
-                                   "(PYTORCH_CUDA_ALLOC_CONF=expandable_segments is not supported)")
+        hbuf = ctypes.create_string_buffer(64)
+        off = ctypes.c_size_t(0)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib.b200gptq_tp_export(self.own.data_ptr(), hbuf, ctypes.byref(off)), "b200gptq_tp_export")
+        handle, offset = hbuf.raw, int(off.value)
         gathered: List[object] = [None] * self.world
         dist.all_gather_object(gathered, (handle, offset, self.device.index), group=group)
         self._mapped: List[int] = []
@@ -86,8 +82,19 @@ class PeerExchange:
         self.own[:4].zero_()
 
     def close(self) -> None:
-        """Unmap the peers' buffers (call when no kernel that uses them is in flight)."""
-        with torch.cuda.device(self.device):
-            for base in self._mapped:
-                _lib.lib.b200gptq_tp_close_peer(base)
-        self._mapped = []
+        """Unmap the peers' buffers.  Collective in spirit: call it on every rank once no kernel that uses the
+        buffers is in flight anywhere (a barrier after the last synchronise), and before the owners free them."""
+        mapped, self._mapped = self._mapped, []
+        if mapped:
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.device(self.device):
+                for base in mapped:
+                    _lib.lib.b200gptq_tp_close_peer(base)
+
+    def __del__(self):
+        import sys
+        if not sys.is_finalizing():
+            try:
+                self.close()
+            except Exception:
+                pass

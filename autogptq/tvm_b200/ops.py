@@ -197,8 +197,9 @@ class GemvPlan:
         return out
 
     def __del__(self):
+        import sys
         h, self._handle = getattr(self, "_handle", None), None
-        if h:
+        if h and not sys.is_finalizing():     # at interpreter exit the host object is reclaimed with the process
             _lib.lib.b200gptq_gemv_plan_destroy(h)
 
 

@@ -192,6 +192,16 @@ class QuantLinear(nn.Module):
             # measured on B200: from 9 rows on, one tensor-core pass (35-45 us for a 4096 x 12288 layer) beats two
             # or more GEMV passes
             y = ops.gemm(x2, *args, **kw)
+        elif M > 64:
+            # no tensor-core kernel for this layout and many rows: dequantise once with the library's kernel (the
+            # reference's own dequantise-then-matmul order, qlinear.py:242-243) and let the dense product run on the
+            # GPU's GEMM library; M / 8 GEMV passes would read the weights M / 8 times
+            _, W = ops.dequantize(self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits,
+                                  self.groupsize, want_q=False)
+            xg = x2 if self._x_perm is None else x2.index_select(1, self._x_perm.long())
+            y = xg @ W
+            if self.bias is not None:
+                y = y + self.bias
         else:
             # 2- and 8-bit layers, and layers whose groups cut through 32-row blocks, have no tensor-core kernel:
             # GEMV passes of up to 8 rows

@@ -21,9 +21,12 @@ format imposes when one linear is split over ranks:
     ``auto_gptq/nn_modules/qlinear.py:242``).  Such a shard has few rows per group, so it runs on the
     general GEMV kernel, not the streaming one.
 
-  (An act-order layer whose input is an element-wise function of a column-parallel layer's output -- fc1 -> fc2,
-  gate/up -> down -- could avoid that by re-ordering its rows by group once and applying the same permutation to
-  the producer's output columns at load time; that is not implemented.)
+* an act-order layer whose input is an element-wise function of a column-parallel layer's output
+  (fc1 -> fc2, gate|up -> down) avoids that: :func:`fold_act_order` re-orders its rows by group once and applies
+  the same permutation to the producer's output columns, after which the consumer is an ordinary layer
+  (``g_idx == k // group_size``) that is cut on group boundaries, streams, and needs no gather of its input.
+  The function computed by the pair does not change.  (o_proj / out_proj cannot use it: their input is laid out by
+  attention head.)
 """
 from __future__ import annotations
 
@@ -91,6 +94,88 @@ def take_rows(layer: PackedLayer, k_a: int, k_b: int, keep_bias: bool) -> Packed
                        layer.g_idx[k_a:k_b].contiguous(), bias)
 
 
+def unpack_fields(words: torch.Tensor, bits: int) -> torch.Tensor:
+    """Inverse of the packing along dim 0: int32 words ``[R/32*bits, C]`` -> fields int32 ``[R, C]``."""
+    w = words.to(torch.int64) & 0xFFFFFFFF
+    if bits in (2, 4, 8):
+        pf = 32 // bits
+        shifts = (torch.arange(pf, device=words.device, dtype=torch.int64) * bits).view(1, pf, 1)
+        f = (w.unsqueeze(1) >> shifts) & ((1 << bits) - 1)
+        return f.reshape(-1, words.shape[1]).to(torch.int32)
+    t = w.reshape(-1, 3, words.shape[1])
+    stream_lo = t[:, 0] | (t[:, 1] << 32)            # bits 0..63 of the 96-bit stream
+    out = []
+    for j in range(32):
+        bit = 3 * j
+        if bit + 3 <= 64:
+            out.append((stream_lo >> bit) & 7)
+        else:
+            hi = t[:, 2]
+            if bit >= 64:
+                out.append((hi >> (bit - 64)) & 7)
+            else:                                     # field 21 straddles bits 63..65
+                out.append(((stream_lo >> bit) & ((1 << (64 - bit)) - 1)) | ((hi & ((1 << (bit + 3 - 64)) - 1)) << (64 - bit)))
+    return torch.stack(out, dim=1).reshape(-1, words.shape[1]).to(torch.int32)
+
+
+def pack_fields_torch(vals: torch.Tensor, bits: int) -> torch.Tensor:
+    """Pack int fields ``[R, C]`` (R % 32 == 0, values < 2**bits) along dim 0 into int32 words, on any device."""
+    R, C = vals.shape
+    v = vals.to(torch.int64)
+    if bits in (2, 4, 8):
+        pf = 32 // bits
+        v = v.reshape(R // pf, pf, C)
+        words = torch.zeros((R // pf, C), dtype=torch.int64, device=vals.device)
+        for j in range(pf):
+            words |= v[:, j] << (bits * j)
+    else:
+        v = v.reshape(R // 32, 32, C)
+        words = torch.zeros((R // 32, 3, C), dtype=torch.int64, device=vals.device)
+        for j in range(32):
+            bit = 3 * j
+            wi, sh = bit // 32, bit % 32
+            words[:, wi] |= (v[:, j] << sh) & 0xFFFFFFFF
+            if sh > 29:
+                words[:, wi + 1] |= v[:, j] >> (32 - sh)
+        words = words.reshape(R // 32 * 3, C)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words)
+    return words.to(torch.int32)
+
+
+def permute_columns(layer: PackedLayer, perm: torch.Tensor, parts: int = 1) -> PackedLayer:
+    """The layer with its output columns re-ordered inside each of its ``parts`` equal blocks: new column ``j`` of a
+    block is old column ``perm[j]`` of that block.  ``qzeros`` is packed along the columns, so its fields are
+    unpacked, moved and packed again."""
+    width = layer.N // parts
+    if perm.numel() != width:
+        raise ValueError("the permutation must cover one block of columns")
+    p = perm.long().to(layer.qweight.device)
+    cols = torch.cat([p + b * width for b in range(parts)])
+    z = unpack_fields(layer.qzeros.t().contiguous(), layer.bits)            # [N, G]
+    qzeros = pack_fields_torch(z.index_select(0, cols).contiguous(), layer.bits).t().contiguous()
+    return PackedLayer(layer.bits, layer.group_size, layer.K, layer.N, layer.qweight.index_select(1, cols).contiguous(),
+                       qzeros, layer.scales.index_select(1, cols).contiguous(), layer.g_idx.clone(),
+                       None if layer.bias is None else layer.bias.index_select(0, cols).contiguous())
+
+
+def fold_act_order(consumer: PackedLayer, producer: PackedLayer, sorted_qweight: torch.Tensor, perm: torch.Tensor,
+                   parts: int = 1) -> Tuple[PackedLayer, PackedLayer]:
+    """Remove the act-order gather of ``consumer``, whose input is an element-wise function of ``producer``'s output
+    (block by block for a fused producer of ``parts`` blocks).  ``perm`` is the stable argsort of the consumer's
+    ``g_idx`` and ``sorted_qweight`` its rows in that order (``ops.sort_rows``); the consumer must have whole groups
+    (every group exactly ``group_size`` rows), so that the sorted ``g_idx`` is ``k // group_size``.  Returns
+    ``(consumer', producer')``: consumer' has ``g_idx == k // group_size`` and expects its input in sorted order,
+    which producer' delivers because its output columns were re-ordered by ``perm``."""
+    gs = _group_size(consumer)
+    g_sorted = consumer.g_idx.long().index_select(0, perm.long())
+    if not torch.equal(g_sorted, torch.arange(consumer.K, device=g_sorted.device) // gs):
+        raise ValueError("the consumer's groups are not whole: sorting its rows does not give k // group_size")
+    folded = PackedLayer(consumer.bits, consumer.group_size, consumer.K, consumer.N, sorted_qweight, consumer.qzeros,
+                         consumer.scales, (torch.arange(consumer.K, device=g_sorted.device) // gs).to(torch.int32),
+                         consumer.bias)
+    return folded, permute_columns(producer, perm, parts)
+
+
 def shard_column(layer: PackedLayer, rank: int, world: int, parts: int = 1,
                  sizes: Optional[Sequence[int]] = None) -> PackedLayer:
     """Column-parallel shard.  ``parts`` > 1: the layer is ``parts`` equal blocks side by side (q|k|v, gate|up) and
@@ -126,4 +211,5 @@ def shard_row(layer: PackedLayer, rank: int, world: int,
     return take_rows(layer, k_a, k_b, keep_bias=(rank == 0)), (k_a, k_b)
 
 
-__all__ = ["split_sizes", "bounds", "is_trivial", "take_columns", "take_rows", "shard_column", "shard_row"]
+__all__ = ["split_sizes", "bounds", "is_trivial", "take_columns", "take_rows", "shard_column", "shard_row",
+           "unpack_fields", "pack_fields_torch", "permute_columns", "fold_act_order"]

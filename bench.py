@@ -296,6 +296,7 @@ def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
            "allreduce": "none" if world == 1 else ("fused peer-memory exchange" if batch <= 8 else "process group")}
     if m.exchange is not None:
         out["exchange_status"] = m.exchange.status()     # 0: no wait of the fused all-reduce ever ran out
+    m.close()
     return out
 
 

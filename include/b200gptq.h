@@ -267,10 +267,12 @@ B200GPTQ_API int b200gptq_tp_status(const void* own_buffer, void* stream, unsign
 /* Let kernels of the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess; fine if it
  * is enabled already).  A host-side set-up call: once per peer before the first exchange. */
 B200GPTQ_API int b200gptq_tp_enable_peer(int peer_device);
-/* Set-up helpers for exchange buffers shared through CUDA IPC: map the allocation behind a 64-byte
- * cudaIpcMemHandle_t (exported by the owning process with cudaIpcGetMemHandle) into the CURRENT device's address
+/* Set-up helpers for exchange buffers shared through CUDA IPC: export the 64-byte cudaIpcMemHandle_t of the
+ * allocation that contains `device_ptr` together with the pointer's offset inside it; map the allocation behind
+ * such a handle into the CURRENT device's address
  * space (`*mapped` = base of that allocation; peer access to the owning device is enabled on the way), unmap it,
  * and read one word through the runtime to check a mapping before kernels use it. */
+B200GPTQ_API int b200gptq_tp_export(const void* device_ptr, void* ipc_handle_out /* 64 bytes */, size_t* offset_out);
 B200GPTQ_API int b200gptq_tp_open_peer(const void* ipc_handle, void** mapped);
 B200GPTQ_API int b200gptq_tp_close_peer(void* mapped);
 B200GPTQ_API int b200gptq_tp_probe(const void* device_ptr, unsigned int* host_out);

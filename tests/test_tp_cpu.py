@@ -89,3 +89,34 @@ def test_split_sizes_and_errors():
         tp.take_rows(act, 16, 48, keep_bias=False)       # cuts must fall on multiples of 32 rows
     with pytest.raises(ValueError):
         tp.take_columns(act, [(0, 48)])                  # and on multiples of 32 columns
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+def test_field_packing_round_trip(bits):
+    w = torch.randint(-2**31, 2**31 - 1, (bits * 4, 40), dtype=torch.int64).to(torch.int32)
+    f = tp.unpack_fields(w, bits)
+    assert torch.equal(tp.pack_fields_torch(f, bits), w)
+    if bits != 8:
+        assert np.array_equal(f.numpy(), O.unpack_qweight(w.numpy(), bits).astype(np.int32))
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+def test_act_order_fold_keeps_the_function(bits):
+    """gate|up -> SiLU*up -> down with an act-order down projection: after the fold the down projection has
+    g_idx == k // group_size and the pair computes what it computed before (oracle weights)."""
+    K, I, N = 256, 512, 96
+    prod = synth.make_layer(bits, K, 2 * I, 128, True, bias=True, seed=1)
+    cons = synth.make_layer(bits, I, N, 128, True, bias=True, seed=2)
+    x = synth.make_x(3, K, seed=1).float()
+
+    def ffn(p, c):
+        u = x @ _dense(p) + p.bias.float()
+        return (torch.nn.functional.silu(u[:, :I]) * u[:, I:]) @ _dense(c) + c.bias.float()
+
+    want = ffn(prod, cons)
+    perm = torch.sort(cons.g_idx.long(), stable=True).indices
+    q = tp.unpack_fields(cons.qweight, bits)
+    qs = tp.pack_fields_torch(q.index_select(0, perm).contiguous(), bits)     # what ops.sort_rows does on the GPU
+    c2, p2 = tp.fold_act_order(cons, prod, qs, perm, parts=2)
+    assert tp.is_trivial(c2)
+    assert torch.allclose(ffn(p2, c2), want, atol=1e-3)

@@ -59,6 +59,20 @@ def gemv_tp_cases(dev, rank, world):
         dist.all_gather(gathered, y)
         assert all(torch.equal(gathered[0], t) for t in gathered), "every rank must hold the same bits"
     assert ex.status() == 0
+    # latency of one exchange of [1, 4096] (printed for the record; no assertion on a shared machine)
+    y = torch.ones((1, 4096), dtype=torch.float16, device=dev)
+    for _ in range(20):
+        ops.tp_allreduce(y.fill_(1.0), ex)
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(200):
+        ops.tp_allreduce(y, ex)
+    e1.record()
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f"exchange latency [1, 4096] x {world} ranks: {e0.elapsed_time(e1) * 1e3 / 200:.2f} us per call", flush=True)
+    assert ex.status() == 0
     return ex
 
 
