@@ -23,6 +23,7 @@ _SIGNATURES = {
     "b200gptq_abi_version": (_c_int, []),
     "b200gptq_dequant": (_c_int, [_c_void_p] * 4 + [_c_int] * 4 + [_c_void_p] * 3),
     "b200gptq_workspace_bytes": (_c_size_t, [_c_int] * 5),
+    "b200gptq_workspace_status": (_c_int, [_c_void_p, _c_void_p, _c_void_p]),
     "b200gptq_gemv": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_gemv_tuned": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_void_p]),
     "b200gptq_gemv_plan_create": (_c_int, [_c_void_p] * 7 + [_c_int] * 7),

@@ -126,6 +126,15 @@ size_t b200gptq_workspace_bytes(int op, int M, int K, int N, int bits) {
     return 0;
 }
 
+int b200gptq_workspace_status(const void* workspace, void* stream, unsigned int* host_out) {
+    if (!workspace || !host_out) return B200GPTQ_ERR_NULL_POINTER;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned int* word = static_cast<const unsigned int*>(workspace) + (kMaxCounters - 1);
+    B200GPTQ_CUDA_TRY(cudaMemcpyAsync(host_out, word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+    B200GPTQ_CUDA_TRY(cudaStreamSynchronize(s));
+    return B200GPTQ_OK;
+}
+
 int b200gptq_gemv_path(int M, int K, int N, int bits, int group_size, int has_g_idx) {
     if (int st = check_layer(K, N, bits, &group_size)) return st;
     if (M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;

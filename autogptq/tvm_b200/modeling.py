@@ -101,6 +101,98 @@ def _parameters_on_meta():
         nn.Module.register_parameter = register
 
 
+def fuse_quant_linears(parts: List[QuantLinear]) -> QuantLinear:
+    """One QuantLinear whose output is the concatenation of the parts' outputs (same input features, bit width,
+    group size and ``g_idx``): ``qweight`` / ``scales`` / ``bias`` are joined along the columns and so are the packed
+    words of ``qzeros`` (every part's width is a multiple of 32 columns = whole words)."""
+    first = parts[0]
+    for p_ in parts[1:]:
+        if (p_.bits, p_.groupsize, p_.infeatures) != (first.bits, first.groupsize, first.infeatures):
+            raise ValueError("layers to fuse must agree in bits, group size and input features")
+        if not torch.equal(p_.g_idx, first.g_idx):
+            raise ValueError("layers to fuse must share g_idx (act-order layers quantised apart cannot be fused)")
+        if (p_.bias is None) != (first.bias is None):
+            raise ValueError("layers to fuse must all have a bias or none")
+    fused = QuantLinear(first.bits, first.groupsize, first.infeatures, sum(p_.outfeatures for p_ in parts),
+                        first.bias is not None)
+    fused.qweight = torch.cat([p_.qweight for p_ in parts], dim=1).contiguous()
+    fused.qzeros = torch.cat([p_.qzeros for p_ in parts], dim=1).contiguous()
+    fused.scales = torch.cat([p_.scales for p_ in parts], dim=1).contiguous()
+    fused.g_idx = first.g_idx.clone()
+    if first.bias is not None:
+        fused.bias = torch.cat([p_.bias for p_ in parts]).contiguous()
+    return fused
+
+
+class _FusedProjection(nn.Module):
+    """Runs the fused layer once per input tensor and hands its column blocks to the stand-ins of the original
+    projections (transformers calls q_proj / k_proj / v_proj -- or gate_proj / up_proj -- with the same tensor)."""
+
+    def __init__(self, fused: QuantLinear, widths: List[int]):
+        super().__init__()
+        self.fused = fused
+        self.bounds = [0]
+        for w in widths:
+            self.bounds.append(self.bounds[-1] + w)
+        self._x = None
+        self._y = None
+        self._served = 0
+
+    def part(self, x, i: int):
+        if self._x is not x:
+            self._y = self.fused(x)
+            self._x, self._served = x, 0
+        y = self._y[..., self.bounds[i]:self.bounds[i + 1]]
+        self._served += 1
+        if self._served == len(self.bounds) - 1:      # every block handed out: drop the references
+            self._x = self._y = None
+        return y
+
+
+class _FusedPart(nn.Module):
+    def __init__(self, owner: _FusedProjection, index: int, holds_owner: bool):
+        super().__init__()
+        if holds_owner:
+            self.owner = owner                      # registered once, so that state_dict / .to() see the fused layer
+        else:
+            object.__setattr__(self, "_owner_ref", owner)
+        self.index = index
+
+    def forward(self, x):
+        owner = self.owner if "owner" in self._modules else self._owner_ref
+        return owner.part(x, self.index)
+
+
+# projections that read the same input and can therefore run as one layer (the reference's own TODO,
+# quantization/opt.py:228)
+FUSABLE = {
+    "llama": [("self_attn", ["q_proj", "k_proj", "v_proj"]), ("mlp", ["gate_proj", "up_proj"])],
+    "opt": [("self_attn", ["q_proj", "k_proj", "v_proj"])],
+}
+
+
+def fuse_projections(model: nn.Module, model_type: str) -> int:
+    """Replace q/k/v (and gate/up) of every decoder layer by one fused QuantLinear each; returns how many were
+    fused.  Layers whose parts cannot be fused (different ``g_idx``) are left as they are."""
+    table = MODEL_TABLES[model_type]
+    done = 0
+    for layer in model.get_submodule(table["layers_block"]):
+        for holder_name, names in FUSABLE.get(model_type, []):
+            holder = getattr(layer, holder_name, None)
+            parts = [getattr(holder, n, None) for n in names] if holder is not None else []
+            if not parts or not all(isinstance(p_, QuantLinear) for p_ in parts):
+                continue
+            try:
+                fused = fuse_quant_linears(parts)
+            except ValueError:
+                continue
+            owner = _FusedProjection(fused, [p_.outfeatures for p_ in parts])
+            for i, n in enumerate(names):
+                setattr(holder, n, _FusedPart(owner, i, holds_owner=(i == 0)))
+            done += 1
+    return done
+
+
 class GPTQModel(nn.Module):
     """Thin wrapper like the reference's ``BaseGPTQForCausalLM``: holds the model and its quantize config."""
 
@@ -137,7 +229,9 @@ class AutoGPTQForCausalLM:
                        use_triton: bool = False, use_tvm: bool = False, export_nnfusion: bool = False,
                        max_memory: Optional[dict] = None, device_map: Optional[str] = None,
                        quantize_config: Optional[BaseQuantizeConfig] = None, model_basename: Optional[str] = None,
-                       trust_remote_code: bool = False) -> GPTQModel:
+                       trust_remote_code: bool = False, fuse_projections: bool = False) -> GPTQModel:
+        """Same arguments as the reference (``_base.py:479-493``) plus ``fuse_projections``: join q/k/v and gate/up
+        of every decoder layer into one QuantLinear each after loading (one N = 3 * hidden launch instead of three)."""
         if use_triton or export_nnfusion or not use_tvm:
             raise NotImplementedError("this package implements the use_tvm=True backend only")
         if max_memory or device_map:
@@ -173,6 +267,8 @@ class AutoGPTQForCausalLM:
         missing = [n for n, p_ in model.named_parameters() if p_.device.type == "meta"]
         if missing:
             raise RuntimeError(f"checkpoint lacks tensors: {missing[:5]}{' ...' if len(missing) > 5 else ''}")
+        if fuse_projections:
+            globals()["fuse_projections"](model, config.model_type)
         model = model.to(device)
         for key in ("max_position_embeddings", "seq_length", "n_positions"):
             if hasattr(model.config, key):
@@ -188,4 +284,5 @@ class AutoGPTQForCausalLM:
         return GPTQModel(model, quantize_config)
 
 
-__all__ = ["AutoGPTQForCausalLM", "BaseQuantizeConfig", "GPTQModel", "make_quant", "find_layers", "SUPPORTED_MODELS"]
+__all__ = ["AutoGPTQForCausalLM", "BaseQuantizeConfig", "GPTQModel", "make_quant", "find_layers", "SUPPORTED_MODELS",
+           "fuse_quant_linears", "fuse_projections"]

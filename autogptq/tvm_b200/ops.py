@@ -33,19 +33,38 @@ def _stream(device: torch.device) -> int:
 
 
 def get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Zero-initialised scratch shared by the calls issued on one device.
+    """Zero-initialised scratch shared by the calls issued on one device AND one stream.
 
-    The kernels restore the scratch to its zero state, so one buffer serves every
-    layer as long as calls are ordered on a stream.  Callers that run layers
-    concurrently on several streams must pass their own workspace instead.
+    The kernels restore the scratch to its zero state, so one buffer serves every layer as long as calls are
+    ordered on a stream; calls on different streams may overlap on the GPU and therefore get different buffers.
+    A buffer that has to grow is replaced (its sticky status word travels to the new one).
     """
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         size = max(nbytes, 1 << 20)
-        ws = torch.zeros(size, dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+        new = torch.zeros(size, dtype=torch.uint8, device=device)
+        if ws is not None:
+            new[16380:16384].copy_(ws[16380:16384])
+        ws = _workspaces[key] = new
     return ws
+
+
+def check_status(device=None) -> None:
+    """Raise if any kernel that used this module's scratch buffers on ``device`` gave up a bounded wait (its results
+    were then undefined).  Synchronises the streams it looks at; meant for tests, benchmarks and the end of a run."""
+    import ctypes
+    for (index, stream), ws in list(_workspaces.items()):
+        if device is not None and torch.device(device).index not in (None, index):
+            continue
+        word = ctypes.c_uint(0)
+        with torch.cuda.device(index):
+            _lib.check(_lib.lib.b200gptq_workspace_status(ws.data_ptr(), stream, ctypes.byref(word)),
+                       "b200gptq_workspace_status")
+        if word.value:
+            raise RuntimeError(f"a kernel on cuda:{index} gave up a bounded wait (status word {word.value}): "
+                               "results computed since the scratch was created are not trustworthy")
 
 
 def layer_dims(qweight: torch.Tensor, bits: int) -> Tuple[int, int]:
@@ -182,15 +201,14 @@ class GemvPlan:
         _lib.check(st, "b200gptq_gemv_plan_create")
         self._handle = handle
         self._need = _lib.workspace_bytes(_lib.OP_GEMV, M, self.K, self.N, bits)
-        self._ws = get_workspace(self.device, self._need)
-        self._ws_ptr, self._ws_bytes = self._ws.data_ptr(), self._ws.numel()
 
     def run(self, x, out=None):
         if not x.is_cuda or x.dtype != torch.float16 or not x.is_contiguous() or tuple(x.shape) != (self.M, self.K):
             raise ValueError(f"x must be a contiguous fp16 CUDA tensor [{self.M}, {self.K}]")
         if out is None:
             out = torch.empty((self.M, self.N), dtype=torch.float16, device=x.device)
-        st = _lib.lib.b200gptq_gemv_plan_run(self._handle, x.data_ptr(), out.data_ptr(), self._ws_ptr, self._ws_bytes,
+        ws = get_workspace(x.device, self._need)      # one buffer per (device, stream)
+        st = _lib.lib.b200gptq_gemv_plan_run(self._handle, x.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(),
                                              torch.cuda.current_stream(x.device).cuda_stream)
         if st:
             _lib.check(st, "b200gptq_gemv_plan_run")

@@ -526,8 +526,12 @@ def main():
             "clocks": clocks,
         }
         line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
-        # sticky status word of the kernels' bounded waits (last word of the counter region): 0 = none ran out
-        line["bounded_waits_expired"] = bool(int(ws[16380:16384].view(torch.int32)[0]) != 0)
+        # sticky status words of the kernels' bounded waits: raises if any wait ever ran out
+        try:
+            ops.check_status(dev)
+            line["bounded_waits_expired"] = False
+        except RuntimeError:
+            line["bounded_waits_expired"] = True
         line.update(extras)
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cfg)

@@ -82,6 +82,15 @@ B200GPTQ_API int b200gptq_dequant(const int32_t* qweight, const int32_t* qzeros,
 B200GPTQ_API size_t b200gptq_workspace_bytes(int op, int M, int K, int N, int bits);
 
 /*
+ * Sticky status word of a scratch buffer.  Every wait inside the kernels is bounded (about 1e9 GPU clock
+ * cycles); a kernel whose wait runs out raises this word to a non-zero value, finishes with undefined results
+ * and returns, so the context stays usable.  The call copies the word to `*host_out` and SYNCHRONISES the
+ * stream.  0 = no wait ever ran out since the buffer was zero-filled.  (The word is the last 32-bit word of
+ * the first 16 KiB of the buffer; b200gptq_gemv_static keeps its scratch private and has no such query.)
+ */
+B200GPTQ_API int b200gptq_workspace_status(const void* workspace, void* stream, unsigned int* host_out);
+
+/*
  * Decode GEMV, 1 <= M <= 8:  y[m,:] = x[m,:] @ W (+ bias), fp32 accumulation,
  * fp16 result.  bits in {2,3,4,8}.  Replaces the TVM `m1` kernel launch of
  * pycuda_warpper.py:144-149 (kernel: src/kernels/gemv_kernel.cu:25-55).

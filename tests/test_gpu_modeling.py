@@ -38,3 +38,19 @@ def test_loaded_model_matches_dense_weights(tmp_path):
     assert (step_q - step_d).abs().max() <= 2e-2 * max(1.0, step_d.abs().max().item())
     out = m.generate(input_ids=ids[:, :4], max_new_tokens=4, do_sample=False)
     assert out.shape == (1, 8)
+
+
+def test_fused_projections_give_the_same_logits(tmp_path):
+    """Load-time q|k|v and gate|up fusion: same logits as the unfused model (bit for bit on the GEMV path, where a
+    column's sum does not depend on its neighbours; within fp16 rounding on the GEMM path)."""
+    _tiny_llama_dir(tmp_path, bits=4, group_size=32, safetensors=True)
+    plain = modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), device="cuda:0", use_safetensors=True, use_tvm=True)
+    fused = modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), device="cuda:0", use_safetensors=True, use_tvm=True,
+                                                        fuse_projections=True)
+    assert fused.model.model.layers[0].self_attn.q_proj.owner.fused.outfeatures == 3 * 64
+    ids = torch.randint(0, 320, (1, 24), generator=torch.Generator().manual_seed(4)).to(DEV)
+    with torch.no_grad():
+        a, b = plain.model(input_ids=ids).logits.float(), fused.model(input_ids=ids).logits.float()
+        a1, b1 = plain.model(input_ids=ids[:, :1]).logits.float(), fused.model(input_ids=ids[:, :1]).logits.float()
+    assert (a - b).abs().max() <= 2e-2 * max(1.0, a.abs().max().item())
+    assert (a1 - b1).abs().max() <= 2e-2 * max(1.0, a1.abs().max().item())

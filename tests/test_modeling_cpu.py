@@ -88,3 +88,30 @@ def test_other_backends_are_refused(tmp_path):
         modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), use_tvm=False)
     with pytest.raises(FileNotFoundError):
         modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), use_tvm=True, model_basename="nope")
+
+
+def test_load_time_fusion_of_projections(tmp_path):
+    """fuse_projections=True: q/k/v and gate/up of every layer become one QuantLinear each whose dequantised weights
+    are the parts' weights side by side (N = 3 * hidden for q|k|v)."""
+    import numpy as np
+    from oracle import gptq_oracle as O
+    cfg, names, saved = _tiny_llama_dir(tmp_path)
+    loaded = modeling.AutoGPTQForCausalLM.from_quantized(str(tmp_path), device="cpu", use_safetensors=True, use_tvm=True,
+                                                         fuse_projections=True)
+
+    def dense(m):
+        return O.dequantize(m.qweight.numpy(), m.qzeros.numpy(), m.scales.numpy(), m.g_idx.numpy(), m.bits)[2]
+
+    layer0, saved0 = loaded.model.model.layers[0], saved.model.layers[0]
+    fused = layer0.self_attn.q_proj.owner.fused
+    assert isinstance(fused, QuantLinear) and fused.outfeatures == 3 * cfg.hidden_size
+    want = np.concatenate([dense(saved0.self_attn.q_proj), dense(saved0.self_attn.k_proj),
+                           dense(saved0.self_attn.v_proj)], axis=1)
+    assert np.array_equal(dense(fused).view(np.uint16), want.view(np.uint16))
+    mlp = layer0.mlp.gate_proj.owner.fused
+    assert mlp.outfeatures == 2 * cfg.intermediate_size
+    want = np.concatenate([dense(saved0.mlp.gate_proj), dense(saved0.mlp.up_proj)], axis=1)
+    assert np.array_equal(dense(mlp).view(np.uint16), want.view(np.uint16))
+    # the fused layers are part of the module tree exactly once
+    n_q = sum(isinstance(m, QuantLinear) for m in loaded.model.modules())
+    assert n_q == cfg.num_hidden_layers * (1 + 1 + 1 + 1)      # qkv, o, gate|up, down

@@ -46,6 +46,20 @@ def test_two_and_more_calls_in_a_row_match_the_caller_scratch_entry_point():
         assert bool(torch.isfinite(got.float()).all())
 
 
+def test_first_use_on_a_side_stream():
+    """The entry point does no clearing of its own (its array is zero-initialised storage), so a call on a
+    non-default, non-blocking stream needs no ordering against the default stream."""
+    layer = synth.make_layer(4, 2048, 1056, 64, True, seed=9, device=DEV)      # general kernel: counters + partial sums
+    x = synth.make_x(2, 2048, seed=9, device=DEV)
+    want = ops.gemv(x, layer.qweight, layer.qzeros, layer.scales, layer.g_idx, 4, 64)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(DEV)
+    with torch.cuda.stream(side):
+        got = ops.gemv_static(x, layer.qweight, layer.qzeros, layer.scales, layer.g_idx, 4, 64)
+    side.synchronize()
+    assert torch.equal(got, want)
+
+
 def test_capacity_is_enforced():
     cap = int(_lib.lib.b200gptq_gemv_static_capacity())
     assert cap == 4 << 20
