@@ -95,11 +95,10 @@ def check(status: int, where: str) -> None:
 
 PATH_STREAM = 1
 PATH_GENERIC = 2
-PATH_STRIP = 3
 
 
 def gemv_path(M: int, K: int, N: int, bits: int, group_size: int, has_g_idx: bool) -> int:
-    """Which kernel ``b200gptq_gemv`` runs: ``PATH_STRIP``, ``PATH_STREAM`` or ``PATH_GENERIC``."""
+    """Which kernel ``b200gptq_gemv`` runs: ``PATH_STREAM`` or ``PATH_GENERIC``."""
     return int(lib.b200gptq_gemv_path(M, K, N, bits, group_size, 1 if has_g_idx else 0))
 
 

@@ -42,15 +42,6 @@ size_t gemm_workspace_bytes(int M, int K, int N, int bits);
 int gemm_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*, const int32_t*,
                   const __half*, __half*, int, int, int, int, int, void*, size_t, cudaStream_t);
 
-bool gemv_strip_supported(int M, int K, int N, int bits, int group_size);
-int gemv_strip_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*, const __half*,
-                        __half*, int, int, int, int, void*, cudaStream_t);
-struct GemvStripPlan;
-GemvStripPlan* gemv_strip_plan_create(const int32_t*, const __half*, bool, int, int, int, int, int*);
-int gemv_strip_plan_run(const GemvStripPlan*, const __half*, const int32_t*, const int32_t*, const __half*, __half*,
-                        void*, cudaStream_t);
-void gemv_strip_plan_destroy(GemvStripPlan*);
-
 struct GemvStreamPlan;
 GemvStreamPlan* gemv_stream_plan_create(const int32_t*, const __half*, bool, int, int, int, int, int, const int*, int*);
 int gemv_stream_plan_run(const GemvStreamPlan*, const __half*, const int32_t*, const int32_t*, const __half*, __half*,
@@ -147,8 +138,8 @@ int b200gptq_workspace_status(const void* workspace, void* stream, unsigned int*
 int b200gptq_gemv_path(int M, int K, int N, int bits, int group_size, int has_g_idx) {
     if (int st = check_layer(K, N, bits, &group_size)) return st;
     if (M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
-    if (has_g_idx || !gemv_stream_supported(M, K, N, bits, group_size)) return B200GPTQ_PATH_GENERIC;
-    return gemv_strip_supported(M, K, N, bits, group_size) ? B200GPTQ_PATH_STRIP : B200GPTQ_PATH_STREAM;
+    return (!has_g_idx && gemv_stream_supported(M, K, N, bits, group_size)) ? B200GPTQ_PATH_STREAM
+                                                                           : B200GPTQ_PATH_GENERIC;
 }
 
 int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
@@ -173,12 +164,6 @@ int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, const int32_t* qz
     if (!aligned16(workspace)) return B200GPTQ_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size)) {
-        // untuned single-row calls on layers that give every SM a strip run the strip kernel; explicit tuning
-        // parameters belong to the cluster kernel and select it
-        if (!slices_per_sm && !ctas_per_sm && gemv_strip_supported(M, K, N, bits, group_size))
-            return gemv_strip_dispatch(static_cast<const __half*>(x), qweight, qzeros,
-                                       static_cast<const __half*>(scales), x_perm, static_cast<const __half*>(bias),
-                                       static_cast<__half*>(y), K, N, bits, group_size, workspace, st);
         const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
         return gemv_stream_dispatch_knobs(static_cast<const __half*>(x), qweight, qzeros,
                                           static_cast<const __half*>(scales), x_perm, static_cast<const __half*>(bias),
@@ -196,8 +181,7 @@ struct b200gptq_gemv_plan {
     const __half *scales, *bias;
     int M, K, N, bits, group_size, slices_per_sm, ctas_per_sm;
     size_t workspace_need;
-    b200gptq::GemvStreamPlan* stream;   // cluster kernel; NULL with `strip` NULL: the general kernel serves this problem
-    b200gptq::GemvStripPlan* strip;     // strip kernel
+    b200gptq::GemvStreamPlan* stream;   // NULL: the general kernel serves this problem
 };
 
 int b200gptq_gemv_plan_create(b200gptq_gemv_plan** out, const int32_t* qweight, const int32_t* qzeros,
@@ -213,13 +197,8 @@ int b200gptq_gemv_plan_create(b200gptq_gemv_plan** out, const int32_t* qweight, 
     if (!p) return B200GPTQ_ERR_CUDA;
     *p = {qweight, qzeros, g_idx, x_perm, static_cast<const __half*>(scales), static_cast<const __half*>(bias),
           M, K, N, bits, group_size, slices_per_sm, ctas_per_sm,
-          b200gptq_workspace_bytes(B200GPTQ_OP_GEMV, M, K, N, bits), nullptr, nullptr};
-    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size) && !slices_per_sm && !ctas_per_sm &&
-        gemv_strip_supported(M, K, N, bits, group_size)) {
-        int st = B200GPTQ_OK;
-        p->strip = gemv_strip_plan_create(qweight, p->scales, x_perm != nullptr, K, N, bits, group_size, &st);
-        if (!p->strip) { delete p; return st; }
-    } else if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size)) {
+          b200gptq_workspace_bytes(B200GPTQ_OP_GEMV, M, K, N, bits), nullptr};
+    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size)) {
         const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
         int st = B200GPTQ_OK;
         p->stream = gemv_stream_plan_create(qweight, p->scales, x_perm != nullptr, M, K, N, bits, group_size,
@@ -236,9 +215,6 @@ int b200gptq_gemv_plan_run(const b200gptq_gemv_plan* p, const void* x, void* y, 
     if (!aligned16(x) || !aligned16(y) || (workspace && !aligned16(workspace))) return B200GPTQ_ERR_ALIGNMENT;
     if (!workspace || workspace_bytes < p->workspace_need) return B200GPTQ_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (p->strip)
-        return gemv_strip_plan_run(p->strip, static_cast<const __half*>(x), p->qzeros, p->x_perm, p->bias,
-                                   static_cast<__half*>(y), workspace, st);
     if (p->stream)
         return gemv_stream_plan_run(p->stream, static_cast<const __half*>(x), p->qzeros, p->x_perm, p->bias,
                                     static_cast<__half*>(y), workspace, st);
@@ -250,7 +226,6 @@ int b200gptq_gemv_plan_run(const b200gptq_gemv_plan* p, const void* x, void* y, 
 void b200gptq_gemv_plan_destroy(b200gptq_gemv_plan* p) {
     if (!p) return;
     if (p->stream) gemv_stream_plan_destroy(p->stream);
-    if (p->strip) gemv_strip_plan_destroy(p->strip);
     delete p;
 }
 

@@ -284,6 +284,117 @@ template <> struct Traits<3> {
     }
 };
 
+// ---------------------------------------------------------------------------------------
+// Integer tensor path of the single-row 3-bit instantiation.  Measured on B200: mma.sync retires one m16n8k32 u8 x s8
+// product in the same 8 cycles per SM sub-partition as one m16n8k16 f16 product (twice the weights), integer and
+// logic instructions issue at half rate, and bytes need far fewer of them than halves: a 96-bit run of 3-bit fields
+// becomes nine operand registers with twelve instructions (bytes q << p, p <= 5) against 23 for halves; the factor
+// 2^p is taken out on the x side.  x is turned into fixed point per
+// unit (X = x * 2^e, |X| < 2^22: exact for every element within 2^-12 of the unit's largest), pre-shifted by what
+// its weight byte lacks, and split into four signed byte planes, which are the columns 0..3 of the B operand: one
+// instruction multiplies 512 weights by all four planes.  The four sums are recombined in fp32 once per unit
+// together with the group's scale; the zero-point term is  zero * sum X.
+//   kSteps      tensor instructions per unit and pair of columns
+//   kPre        log2 of the common factor of (weight byte) * (pre-shifted X) over q * X
+//   item_rows   x preparation: the 8 rows (relative to the unit) that item 4 j + t of a unit handles (quad lane t,
+//               part j) and the left shift each X gets
+// ---------------------------------------------------------------------------------------
+// d += a (u8, 16 x 32) * b (s8, 32 x 8)
+__device__ __forceinline__ void imma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                     uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// exact int -> float for |d| < 2^22 without a conversion instruction (those issue at a fraction of the arithmetic rate)
+__device__ __forceinline__ float small_int_to_float(int d) { return __int_as_float(d + 0x4B400000) - 12582912.f; }
+// 4 x 4 byte transpose: plane p of the result holds byte p of a, b, c, d
+__device__ __forceinline__ void planes_of(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&pl)[4]) {
+    const uint32_t ab01 = __byte_perm(a, b, 0x5140), cd01 = __byte_perm(c, d, 0x5140);
+    const uint32_t ab23 = __byte_perm(a, b, 0x7362), cd23 = __byte_perm(c, d, 0x7362);
+    pl[0] = __byte_perm(ab01, cd01, 0x5410); pl[1] = __byte_perm(ab01, cd01, 0x7632);
+    pl[2] = __byte_perm(ab23, cd23, 0x5410); pl[3] = __byte_perm(ab23, cd23, 0x7632);
+}
+// one step's B operands of a quad lane: [plane][b0, b1]
+__device__ __forceinline__ void store_step(uint8_t* dst, const uint32_t (&lo)[4], const uint32_t (&hi)[4]) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(lo[0], hi[0], lo[1], hi[1]);
+    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(lo[2], hi[2], lo[3], hi[3]);
+}
+struct Table8 { unsigned char v[8]; };
+constexpr unsigned long long pack8b(const Table8& t) {
+    unsigned long long r = 0;
+    for (int i = 0; i < 8; ++i) r |= (unsigned long long)t.v[i] << (8 * i);
+    return r;
+}
+
+// 3-bit: quad lane t owns row block t of the unit (a 96-bit run per column, field f at bit 3 f).  Every byte of the
+// three words holds two whole fields, which two ANDs per word expose as q << p; the eight fields that straddle
+// bytes (2 5 10 13 18 21 26 29) sit at the start of a byte after a shift of the run by 6 bits.  Nine registers hold
+// the 32 fields (and four empty bytes):
+//   R0 = w0 & A: f0 p0, f3 p1, f6 p2, f8 p0      R1 = w0 & B: f1 p3, f4 p4, f7 p5, f9 p3
+//   R2 = w1 & A': f11 p1, f14 p2, f16 p0, f19 p1  R3 = w1 & B': f12 p4, f15 p5, f17 p3, f20 p4
+//   R4 = w2 & A": f22 p2, f24 p0, f27 p1, f30 p2  R5 = w2 & B": f23 p5, f25 p3, f28 p4, f31 p5
+//   R6 = (run >> 6)  : f2 p0, f5 p1, -, f10 p0    R7 = (run >> 38): f13 p1, -, f18 p0, f21 p1
+//   R8 = (run >> 70) : -, f26 p0, f29 p1, -
+// Step s multiplies (R[2s], R[2s+1]); the fifth step has only R8.
+struct IT3 {
+    static constexpr int kSteps = 5, kPre = 5;
+    static constexpr uint32_t m(int p0, int p1, int p2, int p3) {
+        return (p0 < 0 ? 0u : 7u << p0) | (p1 < 0 ? 0u : 7u << (8 + p1)) | (p2 < 0 ? 0u : 7u << (16 + p2)) |
+               (p3 < 0 ? 0u : 7u << (24 + p3));
+    }
+    __device__ static __forceinline__ void unpack(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t (&r)[9]) {
+        r[0] = w0 & m(0, 1, 2, 0); r[1] = w0 & m(3, 4, 5, 3);
+        r[2] = w1 & m(1, 2, 0, 1); r[3] = w1 & m(4, 5, 3, 4);
+        r[4] = w2 & m(2, 0, 1, 2); r[5] = w2 & m(5, 3, 4, 5);
+        r[6] = __funnelshift_r(w0, w1, 6) & m(0, 1, -1, 0);
+        r[7] = __funnelshift_r(w1, w2, 6) & m(1, -1, 0, 1);
+        r[8] = (w2 >> 6) & m(-1, 0, 1, -1);
+    }
+    // items j = 0..2 fill step j; item 3 holds the eight straddling fields, which fill steps 3 and 4
+    __device__ static __forceinline__ void item_rows(int j, int t, int (&row)[8], int (&pre)[8]) {
+        constexpr unsigned long long F0 = pack8b({{0, 3, 6, 8, 1, 4, 7, 9}}), P0 = pack8b({{0, 1, 2, 0, 3, 4, 5, 3}});
+        constexpr unsigned long long F1 = pack8b({{11, 14, 16, 19, 12, 15, 17, 20}}), P1 = pack8b({{1, 2, 0, 1, 4, 5, 3, 4}});
+        constexpr unsigned long long F2 = pack8b({{22, 24, 27, 30, 23, 25, 28, 31}}), P2 = pack8b({{2, 0, 1, 2, 5, 3, 4, 5}});
+        constexpr unsigned long long F3 = pack8b({{2, 5, 10, 13, 18, 21, 26, 29}}), P3 = pack8b({{0, 1, 0, 1, 0, 1, 0, 1}});
+        const unsigned long long f = j == 0 ? F0 : (j == 1 ? F1 : (j == 2 ? F2 : F3));
+        const unsigned long long p = j == 0 ? P0 : (j == 1 ? P1 : (j == 2 ? P2 : P3));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            row[i] = 32 * t + (int)((f >> (8 * i)) & 0xffu);
+            pre[i] = 5 - (int)((p >> (8 * i)) & 0xffu);
+        }
+    }
+    // cur[i] = columns 4g..4g+3 of word-row 3t + i
+    __device__ static __forceinline__ void compute(const uint4 (&cur)[3], const uint8_t* __restrict__ xb, bool has_x,
+                                                   int (&da)[4], int (&db)[4]) {
+        uint2 bx[5];
+#pragma unroll
+        for (int s = 0; s < 5; ++s) {
+            bx[s] = make_uint2(0u, 0u);
+            if (has_x) bx[s] = *reinterpret_cast<const uint2*>(xb + s * 128);
+        }
+#pragma unroll
+        for (int cp = 0; cp < 2; ++cp) {
+            uint32_t ra[9], rb[9];
+            if (cp == 0) { unpack(cur[0].x, cur[1].x, cur[2].x, ra); unpack(cur[0].y, cur[1].y, cur[2].y, rb); }
+            else         { unpack(cur[0].z, cur[1].z, cur[2].z, ra); unpack(cur[0].w, cur[1].w, cur[2].w, rb); }
+            int (&d)[4] = cp == 0 ? da : db;
+            int e[4] = {0, 0, 0, 0};
+            imma(d, ra[0], rb[0], ra[1], rb[1], bx[0].x, bx[0].y);
+            imma(e, ra[2], rb[2], ra[3], rb[3], bx[1].x, bx[1].y);
+            imma(d, ra[4], rb[4], ra[5], rb[5], bx[2].x, bx[2].y);
+            imma(e, ra[6], rb[6], ra[7], rb[7], bx[3].x, bx[3].y);
+            imma(d, ra[8], rb[8], 0u, 0u, bx[4].x, 0u);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) d[r] += e[r];
+        }
+    }
+};
+// bytes of one unit's B operands in shared memory: [step][quad lane][plane][b0, b1]
+constexpr int kIntUnitBytes = IT3::kSteps * 4 * 32;
+
 struct Plan {
     int cgs;          // column groups (256 columns each) = clusters
     int kbs;          // units per column group
@@ -300,7 +411,15 @@ struct Plan {
 
 template <int BITS> __host__ __device__ constexpr int unit_bytes() { return Traits<BITS>::kWordRows * kRowPitch; }
 // Dynamic shared memory, in this order: ring | xs | s_sm | z_sm | ps | part | red
+// x as staged for the tensor instructions: fp16 fragments (several rows of x) or byte planes (one row)
 __host__ __device__ inline int xs_bytes(int S, int M) { return S * M * 256; }
+// The integer path pays for a longer preparation of x with a shorter loop: measured on B200 it wins for 3-bit layers
+// (8.2 against 8.6 us on the 4096 x 11008 benchmark layer) and loses for 4-bit ones, whose fp16 unpacking is cheap
+// (5.5 against 5.0 us on 4096 x 4096).
+template <int BITS> __host__ __device__ constexpr bool int_path(int M) { return M == 1 && BITS == 3; }
+template <int BITS> __host__ __device__ constexpr int xs_total(int S, int M) {
+    return int_path<BITS>(M) ? S * kIntUnitBytes : xs_bytes(S, M);
+}
 __host__ __device__ inline int s_sm_bytes(int gbox) { return gbox * kCgCols * 2; }
 __host__ __device__ inline int z_sm_bytes(int gbox) { return gbox * kCgCols; }
 __host__ __device__ inline int ps_bytes(int S, int M) { return (S * M * 8 + 15) & ~15; }
@@ -343,6 +462,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                    const __half* __restrict__ bias, __half* __restrict__ y, int M_rows, int K, int N,
                    int group_size, Plan plan, unsigned int* __restrict__ status, const __grid_constant__ TpArgs tp) {
     const int M = MULTI ? M_rows : 1;
+    constexpr bool INT = int_path<BITS>(MULTI ? 2 : 1);   // products on the integer tensor path
     constexpr int MM = MULTI ? kMaxM : 1;
     using T = Traits<BITS>;
     constexpr int UB = unit_bytes<BITS>();
@@ -367,8 +487,8 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // the swizzle pattern is a function of the address: the ring starts on a 1024-byte boundary
     uint8_t* ring = dsm + ((1024u - (smem_u32(dsm) & 1023u)) & 1023u);
     uint32_t* xs = reinterpret_cast<uint32_t*>(ring + (size_t)R * UB);
-    const __half* s_sm = reinterpret_cast<const __half*>(reinterpret_cast<uint8_t*>(xs) + xs_bytes(S, M));
-    uint8_t* z_sm = reinterpret_cast<uint8_t*>(xs) + xs_bytes(S, M) + s_sm_bytes(GB);
+    const __half* s_sm = reinterpret_cast<const __half*>(reinterpret_cast<uint8_t*>(xs) + xs_total<BITS>(S, M));
+    uint8_t* z_sm = reinterpret_cast<uint8_t*>(xs) + xs_total<BITS>(S, M) + s_sm_bytes(GB);
     float2* ps = reinterpret_cast<float2*>(z_sm + z_sm_bytes(GB));       // (sum x, sum c*x) per (unit, x row)
     // `part` / `red` hold partial sums at the end of the kernel; before that the same bytes hold the whole of x
     // while it is gathered (PERM with plan.xfull): the other CTAs of the cluster store into `red` only after this
@@ -428,11 +548,14 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         vec_off[r] = L * 128u + (((uint32_t)g ^ (L & 7u)) << 4);
     }
 
-    float out[2][4];   // this lane's columns (2cp, 2cp+1) x rows of x (2j, 2j+1), scaled
+    // several rows of x: this lane's columns (2cp, 2cp+1) x rows of x (2j, 2j+1), scaled; one row: out[0][c] is this
+    // lane's pair of planes of column 4g + c
+    float out[2][4];
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp)
 #pragma unroll
         for (int r = 0; r < 4; ++r) out[cp][r] = 0.f;
+    const float plane_weight = j == 0 ? 1.f : (j == 1 ? 65536.f : 0.f);   // one row: quad lane j holds planes 2j, 2j+1
     float corr[MM];    // column `tid`: offset / zero-point term of every row of x
 #pragma unroll
     for (int m = 0; m < MM; ++m) corr[m] = 0.f;
@@ -486,75 +609,152 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                     }
             }
         }
-        // ---- x: fragment pieces of 8 halves, one per thread and pass ----
-        const int items = nu * M * 16;
-#pragma unroll 1
-        for (int q0 = 0; q0 < items; q0 += kThreads) {
-            const int q = q0 + tid;
-            const bool active = q < items;
-            const int um = q >> 4;
-            const int u = MULTI ? um / M : um, m = MULTI ? um - u * M : 0;
-            int rr[8], pos[8];
-            T::piece_rows((q >> 2) & 3, q & 3, rr, pos);
-            const int row0 = (kb_a + u) * kUnitRows;
-            int kx[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                kx[i] = row0 + rr[i];
-                if (PERM && active) kx[i] = __ldg(x_perm + kx[i]);
+        // Everything before this point uses constants only.  x is the one operand a preceding kernel may still be
+        // writing: under programmatic dependent launch `await_x` is where the kernel waits for it, with its ring,
+        // scales, zero-points and gather indices requested.
+        auto await_x = [&]() {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (plan.early == 0) asm volatile("griddepcontrol.launch_dependents;");
+            if (use_xfull) {
+                // A gather straight from global memory would send every CTA's 2-byte requests to the same few
+                // L2 lines at the same moment; one linear bulk copy of x per CTA and a gather from shared memory
+                // costs the L2 a twelfth of the requests.
+                if (tid == 0) {
+                    const uint32_t row_bytes = (uint32_t)(xrow_halves * 2);
+                    mbar_arrive_expect_tx(x_bar, row_bytes * (uint32_t)M);
+                    for (int mm = 0; mm < M; ++mm)
+                        asm volatile(
+                            "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                            ::"r"(smem_u32(xfull) + mm * row_bytes), "l"(x + (size_t)mm * K + xrow_first),
+                              "r"(row_bytes), "r"(x_bar) : "memory");
+                }
+                mbar_wait(x_bar, 0, &gave_up);
             }
-            if (first && q0 == 0) {
-                // Everything above used constants only.  x is the one operand a preceding kernel may still be
-                // writing: under programmatic dependent launch this is where the kernel waits for it, with its
-                // ring, scales, zero-points and gather indices requested.
-                asm volatile("griddepcontrol.wait;" ::: "memory");
-                if (plan.early == 0) asm volatile("griddepcontrol.launch_dependents;");
+        };
+        if constexpr (!INT) {
+            // ---- x: fragment pieces of 8 halves, one per thread and pass ----
+            const int items = nu * M * 16;
+    #pragma unroll 1
+            for (int q0 = 0; q0 < items; q0 += kThreads) {
+                const int q = q0 + tid;
+                const bool active = q < items;
+                const int um = q >> 4;
+                const int u = MULTI ? um / M : um, m = MULTI ? um - u * M : 0;
+                int rr[8], pos[8];
+                T::piece_rows((q >> 2) & 3, q & 3, rr, pos);
+                const int row0 = (kb_a + u) * kUnitRows;
+                int kx[8];
+    #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    kx[i] = row0 + rr[i];
+                    if (PERM && active) kx[i] = __ldg(x_perm + kx[i]);
+                }
+                if (first && q0 == 0) {
+                    await_x();
+                }
+                unsigned short xv[8];
                 if (use_xfull) {
-                    // A gather straight from global memory would send every CTA's 2-byte requests to the same few
-                    // L2 lines at the same moment; one linear bulk copy of x per CTA and a gather from shared memory
-                    // costs the L2 a twelfth of the requests.
-                    if (tid == 0) {
-                        const uint32_t row_bytes = (uint32_t)(xrow_halves * 2);
-                        mbar_arrive_expect_tx(x_bar, row_bytes * (uint32_t)M);
-                        for (int mm = 0; mm < M; ++mm)
-                            asm volatile(
-                                "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                ::"r"(smem_u32(xfull) + mm * row_bytes), "l"(x + (size_t)mm * K + xrow_first),
-                                  "r"(row_bytes), "r"(x_bar) : "memory");
+    #pragma unroll
+                    for (int i = 0; i < 8; ++i) xv[i] = active ? xfull[m * xrow_halves + kx[i] - xrow_first] : (unsigned short)0;
+                } else {
+    #pragma unroll
+                    for (int i = 0; i < 8; ++i) xv[i] = active ? __ldcg(xu + (size_t)m * K + kx[i]) : (unsigned short)0;
+                }
+                float sx = 0.f, scx = 0.f;
+    #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float xf = __half2float(__ushort_as_half(xv[i]));
+                    sx += xf;
+                    scx = fmaf(__int_as_float((137 - pos[i]) << 23), xf, scx);   // 2^(10 - pos)
+                }
+                if (active) {
+                    uint4 piece;
+                    piece.x = (uint32_t)xv[0] | ((uint32_t)xv[1] << 16);
+                    piece.y = (uint32_t)xv[2] | ((uint32_t)xv[3] << 16);
+                    piece.z = (uint32_t)xv[4] | ((uint32_t)xv[5] << 16);
+                    piece.w = (uint32_t)xv[6] | ((uint32_t)xv[7] << 16);
+                    *reinterpret_cast<uint4*>(xs + 4 * q) = piece;
+                }
+                // the 16 pieces of one (unit, x row) sit in 16 adjacent lanes
+    #pragma unroll
+                for (int o = 1; o < 16; o <<= 1) {
+                    sx += __shfl_xor_sync(0xffffffffu, sx, o);
+                    scx += __shfl_xor_sync(0xffffffffu, scx, o);
+                }
+                if (active && (lane & 15) == 0) ps[um] = make_float2(sx, scx);
+            }
+        } else {
+            // ---- x, one row: fixed point per unit, four signed byte planes in the order of the B operand.  Item
+            //      q = 16 u + 4 j + t of the stage: unit u, quad lane t, part j (8 rows); the 16 items of a unit sit
+            //      in 16 adjacent lanes ----
+            using I = IT3;
+            const int items = nu * 16;
+#pragma unroll 1
+            for (int q0 = 0; q0 < items; q0 += kThreads) {
+                const int q = q0 + tid;
+                const bool active = q < items;
+                const int u = q >> 4, jq = (q >> 2) & 3, tq = q & 3;
+                int rr[8], pre[8];
+                I::item_rows(jq, tq, rr, pre);
+                const int row0 = (kb_a + u) * kUnitRows;
+                int kx[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    kx[i] = row0 + rr[i];
+                    if (PERM && active) kx[i] = __ldg(x_perm + kx[i]);
+                }
+                if (first && q0 == 0) await_x();
+                float xf[8];
+                unsigned int mx = 0u;   // bits of the largest |x|: the order of non-negative floats, NaN above infinity
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    unsigned short h = 0;
+                    if (active) h = use_xfull ? xfull[kx[i] - xrow_first] : __ldcg(xu + kx[i]);
+                    xf[i] = __half2float(__ushort_as_half(h));
+                    mx = max(mx, __float_as_uint(fabsf(xf[i])));
+                }
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                // 2^ex > max |x| of the unit; X = x * 2^(148 - ex) has |X| < 2^22.  A unit of zeros takes any scale; a
+                // unit with an infinity or a NaN gets a NaN factor, so that its columns come out as NaN.
+                int ex = (int)(mx >> 23);
+                const bool bad = ex == 255;
+                if (ex == 0 || bad) ex = 127;
+                const float scale = __uint_as_float((uint32_t)(275 - ex) << 23);
+                int sum = 0;
+                int dg[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    // round to nearest through the fp32 adder: |x * scale| <= 2^22
+                    const int X = __float_as_int(fmaf(xf[i], scale, 12582912.f)) - 0x4B400000;
+                    sum += X;
+                    dg[i] = ((X << pre[i]) + 0x00808080) ^ 0x00808080;   // four signed base-256 digits
+                }
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (active) {
+                    if ((lane & 15) == 0) {
+                        const float delta = __uint_as_float((uint32_t)(ex - 21) << 23);   // 2^(ex - 148)
+                        float cq = __uint_as_float((uint32_t)(ex - 21 - I::kPre) << 23);
+                        if (bad) cq = __uint_as_float(0x7fc00000u);
+                        ps[u] = make_float2(cq, delta * (float)sum);   // (factor of the plane sums, sum of x)
                     }
-                    mbar_wait(x_bar, 0, &gave_up);
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(xs) + (size_t)u * kIntUnitBytes;
+                    uint32_t lo[4], hi[4];
+                    if (jq < 3) {
+                        planes_of(dg[0], dg[1], dg[2], dg[3], lo);
+                        planes_of(dg[4], dg[5], dg[6], dg[7], hi);
+                        store_step(dst + (jq * 4 + tq) * 32, lo, hi);
+                    } else {
+                        planes_of(dg[0], dg[1], 0, dg[2], lo);
+                        planes_of(dg[3], 0, dg[4], dg[5], hi);
+                        store_step(dst + (3 * 4 + tq) * 32, lo, hi);
+                        planes_of(0, dg[6], dg[7], 0, lo);
+                        hi[0] = hi[1] = hi[2] = hi[3] = 0u;
+                        store_step(dst + (4 * 4 + tq) * 32, lo, hi);
+                    }
                 }
             }
-            unsigned short xv[8];
-            if (use_xfull) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) xv[i] = active ? xfull[m * xrow_halves + kx[i] - xrow_first] : (unsigned short)0;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) xv[i] = active ? __ldcg(xu + (size_t)m * K + kx[i]) : (unsigned short)0;
-            }
-            float sx = 0.f, scx = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float xf = __half2float(__ushort_as_half(xv[i]));
-                sx += xf;
-                scx = fmaf(__int_as_float((137 - pos[i]) << 23), xf, scx);   // 2^(10 - pos)
-            }
-            if (active) {
-                uint4 piece;
-                piece.x = (uint32_t)xv[0] | ((uint32_t)xv[1] << 16);
-                piece.y = (uint32_t)xv[2] | ((uint32_t)xv[3] << 16);
-                piece.z = (uint32_t)xv[4] | ((uint32_t)xv[5] << 16);
-                piece.w = (uint32_t)xv[6] | ((uint32_t)xv[7] << 16);
-                *reinterpret_cast<uint4*>(xs + 4 * q) = piece;
-            }
-            // the 16 pieces of one (unit, x row) sit in 16 adjacent lanes
-#pragma unroll
-            for (int o = 1; o < 16; o <<= 1) {
-                sx += __shfl_xor_sync(0xffffffffu, sx, o);
-                scx += __shfl_xor_sync(0xffffffffu, scx, o);
-            }
-            if (active && (lane & 15) == 0) ps[um] = make_float2(sx, scx);
         }
         __syncthreads();   // fragments and sums are in shared memory
         first = false;
@@ -590,7 +790,10 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             const int done_slot = slot;
             if (++slot == R) { slot = 0; ++round; }
             float d[4][4];
-            T::compute(cur, bsm, g < M, d);
+            int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
+            if constexpr (!INT) T::compute(cur, bsm, g < M, d);
+            else IT3::compute(cur, reinterpret_cast<const uint8_t*>(xs) + (size_t)(kb - kb_a) * kIntUnitBytes + j * 32 + g * 8,
+                                   g < 4, da, db);
             if (refill) {
                 before = __shfl_sync(0xffffffffu, before, 0);
                 if (before == kWarps - 1 && lane == 0) {
@@ -604,10 +807,19 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             const uint2 sv = *reinterpret_cast<const uint2*>(s_sm + gl * kCgCols + lane_col);
             const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
             const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
-            out[0][0] = fmaf(s01.x, d[0][0] + d[2][0], out[0][0]); out[0][1] = fmaf(s01.x, d[0][1] + d[2][1], out[0][1]);
-            out[0][2] = fmaf(s01.y, d[0][2] + d[2][2], out[0][2]); out[0][3] = fmaf(s01.y, d[0][3] + d[2][3], out[0][3]);
-            out[1][0] = fmaf(s23.x, d[1][0] + d[3][0], out[1][0]); out[1][1] = fmaf(s23.x, d[1][1] + d[3][1], out[1][1]);
-            out[1][2] = fmaf(s23.y, d[1][2] + d[3][2], out[1][2]); out[1][3] = fmaf(s23.y, d[1][3] + d[3][3], out[1][3]);
+            if constexpr (!INT) {
+                out[0][0] = fmaf(s01.x, d[0][0] + d[2][0], out[0][0]); out[0][1] = fmaf(s01.x, d[0][1] + d[2][1], out[0][1]);
+                out[0][2] = fmaf(s01.y, d[0][2] + d[2][2], out[0][2]); out[0][3] = fmaf(s01.y, d[0][3] + d[2][3], out[0][3]);
+                out[1][0] = fmaf(s23.x, d[1][0] + d[3][0], out[1][0]); out[1][1] = fmaf(s23.x, d[1][1] + d[3][1], out[1][1]);
+                out[1][2] = fmaf(s23.y, d[1][2] + d[3][2], out[1][2]); out[1][3] = fmaf(s23.y, d[1][3] + d[3][3], out[1][3]);
+            } else {
+                // recombine this lane's two planes (sums S_p of plane p: 256^p S_p), scale by the unit's factor and the group's scale
+                const float c = ps[kb - kb_a].x * plane_weight;
+                out[0][0] = fmaf(s01.x * c, fmaf(256.f, small_int_to_float(da[1]), small_int_to_float(da[0])), out[0][0]);
+                out[0][1] = fmaf(s01.y * c, fmaf(256.f, small_int_to_float(da[3]), small_int_to_float(da[2])), out[0][1]);
+                out[0][2] = fmaf(s23.x * c, fmaf(256.f, small_int_to_float(db[1]), small_int_to_float(db[0])), out[0][2]);
+                out[0][3] = fmaf(s23.y * c, fmaf(256.f, small_int_to_float(db[3]), small_int_to_float(db[2])), out[0][3]);
+            }
             if (--left == 0) { ++gl; left = units_per_group; }
         }
 
@@ -623,7 +835,8 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 for (int m = 0; m < MM; ++m)
                     if (m < M) {
                         const float2 p = ps[u * M + m];
-                        corr[m] = fmaf(sg, fmaf(zg, p.x, p.y), corr[m]);
+                        if constexpr (!INT) corr[m] = fmaf(sg, fmaf(zg, p.x, p.y), corr[m]);
+                        else corr[m] = fmaf(sg * zg, p.y, corr[m]);   // one row: zero * sum x
                     }
                 if (--lc == 0) { ++gc; lc = units_per_group; }
             }
@@ -631,13 +844,25 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     }
 
     // ---- this CTA's partial result: lane layout -> one column per thread, minus the offset term ----
+    if constexpr (!INT) {
 #pragma unroll
-    for (int cp = 0; cp < 2; ++cp)
+        for (int cp = 0; cp < 2; ++cp)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int m = 2 * j + (r & 1);
-            if (m < M) part[m * kCgCols + lane_col + 2 * cp + (r >> 1)] = out[cp][r];
+            for (int r = 0; r < 4; ++r) {
+                const int m = 2 * j + (r & 1);
+                if (m < M) part[m * kCgCols + lane_col + 2 * cp + (r >> 1)] = out[cp][r];
+            }
+    } else {
+        // one row: the quad's lanes hold different planes of the same four columns
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float v = out[0][c];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            out[0][c] = v;
         }
+        if (j == 0) *reinterpret_cast<float4*>(part + lane_col) = make_float4(out[0][0], out[0][1], out[0][2], out[0][3]);
+    }
     __syncthreads();
     const int n = cg * kCgCols + tid;
     // The column group's sums over all of K end up in v[] of ONE CTA (the only one of a group, or the cluster's
@@ -763,7 +988,7 @@ Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* kn
     if (c < 1) c = 1;
     p.cluster = c;
     const int longest = (p.kbs + c - 1) / c;
-    p.stage_units = kXsBytes / (M * 256);
+    p.stage_units = int_path<BITS>(M) ? kXsBytes / kIntUnitBytes : kXsBytes / (M * 256);
     if (p.stage_units > longest) p.stage_units = longest;
     p.group_box = max_groups_per_stage(p, group_size);
     p.push = (c > 1 && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
@@ -777,7 +1002,7 @@ Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* kn
     int tail = part_bytes(M) + (p.push ? red_bytes(M, c) : 0);
     if (p.xfull == 2) tail += xcopy_bytes;
     if (p.xfull == 1 && tail < xcopy_bytes) tail = xcopy_bytes;
-    const int fixed = xs_bytes(p.stage_units, M) + s_sm_bytes(p.group_box) + z_sm_bytes(p.group_box) +
+    const int fixed = xs_total<BITS>(p.stage_units, M) + s_sm_bytes(p.group_box) + z_sm_bytes(p.group_box) +
                       ps_bytes(p.stage_units, M) + tail + 1024;
     // Footprint: as many CTAs per SM as still let a CTA hold its whole slice (at least two); CTAs of the next launch
     // of the stream find room beside the running ones and fetch their weights early.

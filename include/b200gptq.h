@@ -150,17 +150,14 @@ B200GPTQ_API int b200gptq_gemv_plan_run(const b200gptq_gemv_plan* plan, const vo
 B200GPTQ_API void b200gptq_gemv_plan_destroy(b200gptq_gemv_plan* plan);
 
 /*
- * Which kernel b200gptq_gemv runs for this problem: B200GPTQ_PATH_STRIP (one row of x, a layer wide enough
- * to give every multiprocessor a 32-column strip: integer tensor path, no combine between thread blocks),
- * B200GPTQ_PATH_STREAM (the cluster kernel: up to 8 rows, any width; also what explicit tuning parameters
- * of b200gptq_gemv_tuned select) or B200GPTQ_PATH_GENERIC (a negative B200GPTQ_ERR_* code for an invalid
- * problem).  Host-only; launches nothing.  has_g_idx != 0 means a non-NULL g_idx is passed.
+ * Which kernel b200gptq_gemv runs for this problem: B200GPTQ_PATH_STREAM or
+ * B200GPTQ_PATH_GENERIC (a negative B200GPTQ_ERR_* code for an invalid problem).
+ * Host-only; launches nothing.  has_g_idx != 0 means a non-NULL g_idx is passed.
  * The reference picks its kernel per (bits, N, K, M bucket) in
  * pycuda_warpper.py:138-189; this is the query for the same decision here.
  */
 #define B200GPTQ_PATH_STREAM 1
 #define B200GPTQ_PATH_GENERIC 2
-#define B200GPTQ_PATH_STRIP 3
 B200GPTQ_API int b200gptq_gemv_path(int M, int K, int N, int bits, int group_size, int has_g_idx);
 
 /*

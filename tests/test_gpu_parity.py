@@ -114,16 +114,6 @@ GEMV_CASES = [
 ]
 
 
-def _strip_expected(M, K, N, bits, gs):
-    """The library's rule for the strip kernel, restated: one row of x, 3/4-bit, whole 128-row units per group, K up
-    to 8192, and between 3/4 of a strip and 6 strips of 32 columns per multiprocessor."""
-    sms = torch.cuda.get_device_properties(0).multi_processor_count
-    strips = N // 32
-    g = K if gs == -1 else gs
-    return (M == 1 and bits in (3, 4) and K % 128 == 0 and g % 128 == 0 and K <= 8192 and 4 * strips >= 3 * sms
-            and -(-strips // sms) <= 6)
-
-
 def _trivial_g_idx(layer):
     gs = layer.group_size if layer.group_size != -1 else layer.K
     return bool(torch.equal(layer.g_idx.long(), torch.arange(layer.K) // gs))
@@ -147,10 +137,7 @@ def test_gemv_vs_oracle(bits, K, N, gs, act, bias, M, explicit_g_idx):
     g = d.g_idx if explicit_g_idx else None
     path = _lib.gemv_path(M, K, N, bits, gs, g is not None)
     streams = (not explicit_g_idx) and bits in (3, 4) and K % 128 == 0 and (gs == -1 or gs % 128 == 0)
-    if streams:
-        assert path == (_lib.PATH_STRIP if _strip_expected(M, K, N, bits, gs) else _lib.PATH_STREAM)
-    else:
-        assert path == _lib.PATH_GENERIC
+    assert path == (_lib.PATH_STREAM if streams else _lib.PATH_GENERIC)
     y = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, g, bits, gs, bias=d.bias)
     _check_output(y, x.numpy(), W, None if layer.bias is None else layer.bias.numpy())
     y2 = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, g, bits, gs, bias=d.bias)
@@ -179,36 +166,29 @@ def test_streaming_gemv_vs_oracle(bits, K, N, gs, bias, M):
     x = synth.make_x(M, K, seed=10 + M)
     _, _, W = O.dequantize(*_layer_np(layer), bits)
     d = layer.to(DEV)
-    # explicit tuning parameters select the cluster kernel whatever the shape: this test is about its work split
-    assert _lib.gemv_path(M, K, N, bits, gs, False) in (_lib.PATH_STREAM, _lib.PATH_STRIP)
-    y = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias, tuning=(3, 3))
+    assert _lib.gemv_path(M, K, N, bits, gs, False) == _lib.PATH_STREAM
+    y = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias)
     _check_output(y, x.numpy(), W, None if layer.bias is None else layer.bias.numpy())
-    y2 = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias, tuning=(3, 3))
+    y2 = ops.gemv(x.to(DEV), d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias)
     assert torch.equal(y, y2)
 
 
-STRIP_CASES = [
-    # bits, K, N, gs, act, bias : single-row shapes the strip kernel takes
-    (4, 4096, 4096, 128, False, True),       # config 0: fewer strips than multiprocessors
-    (3, 4096, 11008, 128, True, False),      # config 1: three strips on some multiprocessors, two on the others
+SINGLE_ROW_CASES = [
+    # bits, K, N, gs, act, bias : one row of x; the 3-bit ones run on the integer tensor path (x in fixed point per
+    # 128 rows of K, four byte planes), the 4-bit ones on fp16 fragments
+    (3, 4096, 11008, 128, True, False),      # config 1
     (3, 4096, 11008, 128, False, True),
     (4, 4096, 12288, 128, True, False),      # fused q|k|v
-    (4, 8192, 4096, 128, False, False),      # two passes of the x preparation
     (3, 8192, 8192, 1024, True, True),       # groups of 8 units
-    (4, 2048, 6400, -1, False, True),        # one group over all rows
-    (3, 4096, 4736, 256, False, False),      # exactly one strip per multiprocessor on a 148-SM part
-    (4, 1024, 28416, 128, False, False),     # six strips per multiprocessor, one TMA box per strip
-    (3, 1152, 3584, 128, True, False),       # 9 units: a partly filled second box
-    (4, 128, 8192, 128, False, True),        # one unit
+    (3, 2048, 6400, -1, False, True),        # one group over all rows
+    (3, 1152, 3584, 128, True, False),       # 9 units
+    (3, 128, 8192, 128, False, True),        # one unit
+    (3, 36864, 512, 128, True, False),       # slices longer than one stage of x, through a gather
 ]
 
 
-@pytest.mark.parametrize("bits,K,N,gs,act,bias", STRIP_CASES)
-def test_strip_gemv_vs_oracle(bits, K, N, gs, act, bias):
-    """The strip kernel (integer tensor path, x in fixed point per 128 rows) against the oracle, run twice, and
-    against the cluster kernel on the same inputs."""
-    if not _strip_expected(1, K, N, bits, gs):
-        pytest.skip("this device's multiprocessor count puts the shape outside the strip kernel's range")
+@pytest.mark.parametrize("bits,K,N,gs,act,bias", SINGLE_ROW_CASES)
+def test_single_row_gemv_vs_oracle(bits, K, N, gs, act, bias):
     layer = synth.make_layer(bits, K, N, gs, act, bias=bias, seed=7 * K + N + bits)
     x = synth.make_x(1, K, seed=21)
     _, _, W = O.dequantize(*_layer_np(layer), bits)
@@ -217,24 +197,23 @@ def test_strip_gemv_vs_oracle(bits, K, N, gs, act, bias):
         qw, perm, _ = ops.sort_rows(d.qweight, d.g_idx, bits)
     else:
         qw, perm = d.qweight, None
-    assert _lib.gemv_path(1, K, N, bits, gs, False) == _lib.PATH_STRIP
+    assert _lib.gemv_path(1, K, N, bits, gs, False) == _lib.PATH_STREAM
     b = None if layer.bias is None else layer.bias.numpy()
     y = ops.gemv(x.to(DEV), qw, d.qzeros, d.scales, None, bits, gs, x_perm=perm, bias=d.bias)
     _check_output(y, x.numpy(), W, b)
     assert torch.equal(y, ops.gemv(x.to(DEV), qw, d.qzeros, d.scales, None, bits, gs, x_perm=perm, bias=d.bias))
     plan = ops.GemvPlan(qw, d.qzeros, d.scales, None, perm, d.bias, 1, bits, gs)
     assert torch.equal(plan.run(x.to(DEV)), y)
-    _check_output(ops.gemv(x.to(DEV), qw, d.qzeros, d.scales, None, bits, gs, x_perm=perm, bias=d.bias, tuning=(3, 3)),
+    _check_output(ops.gemv(x.to(DEV), qw, d.qzeros, d.scales, None, bits, gs, x_perm=perm, bias=d.bias, tuning=(2, 3)),
                   x.numpy(), W, b)
     ops.check_status(DEV)
 
 
-def test_strip_gemv_value_ranges():
-    """x is converted to fixed point per 128 rows of K: rows of zeros, a wide dynamic range inside a unit, values
-    at the ends of the fp16 range and a NaN must all come out as the reference's fp32 accumulation would."""
-    bits, K, N, gs = 4, 4096, 4736, 128
-    if not _strip_expected(1, K, N, bits, gs):
-        pytest.skip("outside the strip kernel's range on this device")
+def test_single_row_value_ranges():
+    """On the integer tensor path x is converted to fixed point per 128 rows of K: rows of zeros, a wide dynamic
+    range inside a unit, values at the ends of the fp16 range and a NaN must all come out as fp32 accumulation
+    would give them."""
+    bits, K, N, gs = 3, 4096, 4736, 128
     layer = synth.make_layer(bits, K, N, gs, False, seed=99)
     _, _, W = O.dequantize(*_layer_np(layer), bits)
     d = layer.to(DEV)
