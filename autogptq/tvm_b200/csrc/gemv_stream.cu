@@ -107,13 +107,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same test with a suspend-time hint: the thread may stay suspended for up to `ns` nanoseconds and is woken when
+// the phase completes, so a waiting warp leaves its scheduler's issue slots to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 // Bounded wait.  After ~1e9 clocks, or once any thread of the CTA has given up, waiting stops for
 // good: the kernel then finishes with undefined results and a raised status word instead of hanging.
 __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* gave_up) {
     const long long t0 = clock64();
     while (!*gave_up) {
-        for (int i = 0; i < 32; ++i)
-            if (mbar_try_wait(bar, parity)) return;
+        for (int i = 0; i < 8; ++i)
+            if (mbar_try_wait_for(bar, parity, 2000u)) return;
         if (clock64() - t0 > 1000000000LL) *gave_up = 1;
     }
 }
