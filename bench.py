@@ -342,6 +342,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--min-timed-ms", type=float, default=MIN_TIMED_MS,
+                    help="shortest timed region of the headline (profiling runs pass 0 to keep the launch count small)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip config 0, the GEMM sweep and the decode run")
     ap.add_argument("--no-opt66b", action="store_true",
@@ -429,7 +431,7 @@ def main():
     t = torch.tensor([e0.elapsed_time(e1) / 10], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    passes = max(1, int(-(-MIN_TIMED_MS // (float(t[0]) * args.steps))))
+    passes = max(1, int(-(-args.min_timed_ms // (float(t[0]) * args.steps))))
 
     sampler = ClockSampler(local_rank)
     sampler.start()
