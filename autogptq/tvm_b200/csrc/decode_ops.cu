@@ -5,6 +5,7 @@
 // end2end/autogptq-generation-inference-benchmark.py:26-49).  All are memory-trivial; the point is
 // launch count.  fp16 storage, fp32 arithmetic.
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -321,6 +322,60 @@ act_kernel(const __half* __restrict__ u, __half* __restrict__ act, int I, int ga
     *reinterpret_cast<__half2*>(act + idx) = __floats2half2_rn(r.x, r.y);
 }
 
+// y[m, n] = sum_k x[m, k] * w[n, k]: the dense fp16 vocabulary projection of a decode step (up to 8 rows of x),
+// a pure stream of w.  x is staged in shared memory; a warp takes four rows of w at a time, a lane 16 bytes of
+// each per step; eight products are accumulated in half2 (four HFMA2), then widened and summed in fp32.
+template <int MM>
+__global__ void __launch_bounds__(256)
+dense_gemv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __half* __restrict__ y, int M, int K,
+                  int N) {
+    extern __shared__ __align__(16) unsigned char dense_smem[];
+    __half* xs = reinterpret_cast<__half*>(dense_smem);
+    pdl_enter();
+    const int tid = threadIdx.x, lane = tid & 31;
+    for (int i = tid; i < M * K / 8; i += 256) reinterpret_cast<uint4*>(xs)[i] = reinterpret_cast<const uint4*>(x)[i];
+    __syncthreads();
+    const int gw = blockIdx.x * 8 + (tid >> 5), nw = gridDim.x * 8;
+    for (int n0 = gw * 4; n0 < N; n0 += nw * 4) {
+        float acc[4][MM];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int m = 0; m < MM; ++m) acc[r][m] = 0.f;
+        for (int k = lane * 8; k < K; k += 256) {
+            uint4 wv[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                wv[r] = make_uint4(0u, 0u, 0u, 0u);
+                if (n0 + r < N) wv[r] = __ldcs(reinterpret_cast<const uint4*>(w + (size_t)(n0 + r) * K + k));
+            }
+#pragma unroll
+            for (int m = 0; m < MM; ++m) {
+                if (m >= M) break;
+                const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)m * K + k);
+                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const __half2* wh = reinterpret_cast<const __half2*>(&wv[r]);
+                    __half2 p = __hmul2(wh[0], xh[0]);
+                    p = __hfma2(wh[1], xh[1], p);
+                    p = __hfma2(wh[2], xh[2], p);
+                    p = __hfma2(wh[3], xh[3], p);
+                    const float2 f = __half22float2(p);
+                    acc[r][m] += f.x + f.y;
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int m = 0; m < MM; ++m) {
+                const float v = warp_sum(acc[r][m]);
+                if (lane == 0 && m < M && n0 + r < N) y[(size_t)m * N + n0 + r] = __float2half_rn(v);
+            }
+    }
+}
+
 }  // namespace
 }  // namespace b200gptq
 
@@ -381,6 +436,38 @@ B200GPTQ_API int b200gptq_act(const void* u, void* act, int rows, int I, int gat
     const unsigned blocks = (unsigned)((total / 2 + 255) / 256);
     B200GPTQ_CUDA_TRY(launch_pdl(act_kernel, dim3(blocks), dim3(256), 0, stream, 1, static_cast<const __half*>(u),
                                  static_cast<__half*>(act), I, gated, total));
+    return B200GPTQ_OK;
+}
+
+B200GPTQ_API int b200gptq_dense_gemv(const void* x, const void* w, void* y, int rows, int K, int N, void* stream) {
+    if (!x || !w || !y) return B200GPTQ_ERR_NULL_POINTER;
+    if (rows < 1 || rows > 8 || K <= 0 || N <= 0 || K % 8 != 0 || (size_t)rows * K * 2 > 96 * 1024) return B200GPTQ_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) return B200GPTQ_ERR_ALIGNMENT;
+    const size_t smem = (size_t)rows * K * 2;
+    int blocks = (N + 31) / 32;                     // a CTA's eight warps take 32 rows of w per round
+    if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+    const __half* xh = static_cast<const __half*>(x);
+    const __half* wh = static_cast<const __half*>(w);
+    __half* yh = static_cast<__half*>(y);
+    if (rows == 1) {
+        static std::once_flag once[64];
+        int dev = 0;
+        B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64)
+            std::call_once(once[dev], [] {
+                cudaFuncSetAttribute(dense_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            });
+        B200GPTQ_CUDA_TRY(launch_pdl(dense_gemv_kernel<1>, dim3(blocks), dim3(256), smem, stream, 1, xh, wh, yh, rows, K, N));
+    } else {
+        static std::once_flag once8[64];
+        int dev = 0;
+        B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64)
+            std::call_once(once8[dev], [] {
+                cudaFuncSetAttribute(dense_gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            });
+        B200GPTQ_CUDA_TRY(launch_pdl(dense_gemv_kernel<8>, dim3(blocks), dim3(256), smem, stream, 1, xh, wh, yh, rows, K, N));
+    }
     return B200GPTQ_OK;
 }
 

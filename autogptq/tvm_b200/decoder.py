@@ -60,6 +60,24 @@ OPT_66B = DecoderConfig(arch="opt", layers=64, hidden=9216, heads=72, inter=3686
                         group_size=128, desc_act=True, max_seq=256)
 
 
+def graph_kernels(dot_path: str) -> dict:
+    """Kernel nodes of a captured decode step by function name (from the DOT dump of the CUDA graph): what one token
+    launches, and the evidence that no library collective is among them."""
+    import re
+    counts: dict = {}
+    with open(dot_path) as f:
+        text = f.read()
+    for label in re.findall(r'label="([^"]*)"', text):
+        if "KERNEL" not in label.upper():
+            continue
+        fields = [t.strip() for t in re.split(r"[|{}]|\\[nl]", label) if t.strip()]
+        names = [t for t in fields if re.search(r"[A-Za-z_]\w*(::|<|_kernel|Kernel)", t) or "(" in t]
+        name = max(names, key=len) if names else (fields[-1] if fields else "?")
+        name = re.sub(r"\(.*", "", name).strip()
+        counts[name] = counts.get(name, 0) + 1
+    return counts
+
+
 def check_positions(pos: int, steps: int, max_seq: int) -> None:
     """Refuse a run that would step past the KV caches: the kernels take the position from device memory (so that a
     captured graph can advance it), which leaves this host-side check as the place where a bad request is reported."""
@@ -182,7 +200,7 @@ class GPTQDecoder:
         sl = head_t[lo:lo + self.vocab_local]
         if sl.shape[0] < self.vocab_local:   # the last rank's padding columns
             sl = torch.cat([sl, torch.zeros(self.vocab_local - sl.shape[0], cfg.hidden, device=dev, dtype=torch.float16)])
-        self.lm_head = sl.t().contiguous()
+        self.lm_head = sl.contiguous()          # [vocab_local, hidden]: rows of the projection, streamed once per step
         del head_t
         hd = cfg.head_dim
         for L in self.layers:
@@ -261,7 +279,15 @@ class GPTQDecoder:
     def _sample(self, x_last):
         h = self._norm(x_last, self.final_norm_w, self.final_norm_b)
         self.last_hidden = h
-        return self._pick(h @ self.lm_head)                                    # [B, vocab_local]
+        return self._pick(self._project(h))                                    # [B, vocab_local]
+
+    def _project(self, h):
+        """Vocabulary projection of this rank's slice: the library's dense GEMV for a decode batch, the framework's
+        GEMM for more rows."""
+        h = h.reshape(-1, self.cfg.hidden)
+        if h.shape[0] <= 8:
+            return ops.dense_gemv(h.contiguous(), self.lm_head)
+        return h @ self.lm_head.t()
 
     def _pick(self, logits):
         logits = logits.float()
@@ -343,12 +369,13 @@ class GPTQDecoder:
             delta = self._row(L.down, a)
         ops.add_norm(x, delta, self.final_norm_w, self.final_norm_b, h, eps, rms)
         self.last_hidden = h
-        logits = h @ self.lm_head
+        logits = self._project(h)
         self.tokens.copy_(self._pick(logits))
         self.pos.add_(1)
 
-    def capture(self):
-        """Warm up (allocates scratch, builds run-time views) and capture one decode step in a CUDA graph."""
+    def capture(self, dot_path: Optional[str] = None):
+        """Warm up (allocates scratch, builds run-time views) and capture one decode step in a CUDA graph.
+        ``dot_path``: also write the captured graph in DOT form there (``graph_kernels`` reads it back)."""
         check_positions(self._pos_host, 3, self.cfg.max_seq)   # two warm-up steps and the captured one
         saved_pos, saved_tok = self.pos.clone(), self.tokens.clone()
         s = torch.cuda.Stream(self.device)
@@ -359,8 +386,12 @@ class GPTQDecoder:
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         self.graph = torch.cuda.CUDAGraph()
+        if dot_path:
+            self.graph.enable_debug_mode()
         with torch.cuda.graph(self.graph):
             self._decode_step()
+        if dot_path:
+            self.graph.debug_dump(dot_path)
         self.pos.copy_(saved_pos)
         self.tokens.copy_(saved_tok)
 

@@ -8,6 +8,8 @@ exchange itself is done by the library's kernels.
 """
 from __future__ import annotations
 
+import sys
+
 import ctypes
 from typing import List
 
@@ -91,9 +93,8 @@ class PeerExchange:
                 for base in mapped:
                     _lib.lib.b200gptq_tp_close_peer(base)
 
-    def __del__(self):
-        import sys
-        if not sys.is_finalizing():
+    def __del__(self, _finalizing=sys.is_finalizing):
+        if not _finalizing():
             try:
                 self.close()
             except Exception:

@@ -6,6 +6,7 @@ status.  Nothing here computes on the host.
 """
 from __future__ import annotations
 
+import sys
 from typing import Optional, Tuple
 
 import torch
@@ -214,10 +215,9 @@ class GemvPlan:
             _lib.check(st, "b200gptq_gemv_plan_run")
         return out
 
-    def __del__(self):
-        import sys
+    def __del__(self, _finalizing=sys.is_finalizing):
         h, self._handle = getattr(self, "_handle", None), None
-        if h and not sys.is_finalizing():     # at interpreter exit the host object is reclaimed with the process
+        if h and not _finalizing():     # at interpreter exit the host object is reclaimed with the process
             _lib.lib.b200gptq_gemv_plan_destroy(h)
 
 
@@ -323,4 +323,19 @@ def act(u, out, inter: int, gated: bool):
     with torch.cuda.device(u.device):
         st = _lib.lib.b200gptq_act(_ptr(u), _ptr(out), u.shape[0], inter, 1 if gated else 0, _stream(u.device))
     _lib.check(st, "b200gptq_act")
+    return out
+
+
+def dense_gemv(x, w, out=None):
+    """``y = x @ w.T`` for up to 8 rows of ``x`` (fp16 ``[M, K]``) and a dense fp16 ``w`` ``[N, K]``: the vocabulary
+    projection of a decode step as one pass over ``w`` (``b200gptq_dense_gemv``)."""
+    _need_cuda("x", x, torch.float16)
+    _need_cuda("w", w, torch.float16)
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or not 1 <= x.shape[0] <= 8:
+        raise ValueError("dense_gemv: x [M <= 8, K] and w [N, K] expected")
+    if out is None:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.lib.b200gptq_dense_gemv(_ptr(x), _ptr(w), _ptr(out), x.shape[0], x.shape[1], w.shape[0], _stream(x.device))
+    _lib.check(st, "b200gptq_dense_gemv")
     return out

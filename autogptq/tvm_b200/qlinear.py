@@ -168,6 +168,15 @@ class QuantLinear(nn.Module):
 
     # ---- forward --------------------------------------------------------------------------
     def forward(self, x):
+        if torch.compiler.is_compiling():
+            # Traced: one opaque, shape-inferable operator per layer (torch_ops.py).  The run-time layout must exist
+            # already (post_init(), which from_quantized and the first eager call run); the prepared plans below are
+            # for eager calls.
+            from .torch_ops import quant_matmul
+            x2 = x.half().reshape(-1, self.infeatures).contiguous()
+            y = quant_matmul(x2, self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self._x_perm,
+                             self.bias, self.bits, self.groupsize, self._gemm_ok)
+            return y.reshape(x.shape[:-1] + (self.outfeatures,))
         if not x.is_cuda:
             raise RuntimeError("QuantLinear.forward needs CUDA tensors: this backend has no CPU path")
         if not self._ready():

@@ -309,6 +309,14 @@ B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const 
                                       void* stream);
 B200GPTQ_API int b200gptq_act(const void* u, void* act, int rows, int I, int gated, void* stream);
 
+/*
+ * Dense fp16 projection of up to 8 rows:  y[rows, N] = x[rows, K] @ w[N, K]^T  (fp32 sums of 8-product fp16 partial
+ * sums, one fp16 rounding).  This is the vocabulary projection of a decode step, which AutoGPTQ leaves unquantised
+ * (auto_gptq/modeling/_base.py:534 keeps `lm_head` out of the quantised modules): one pass over w at stream rate,
+ * launched like the other decode-step helpers.  K % 8 == 0, rows * K * 2 <= 96 KiB, x and w 16-byte aligned.
+ */
+B200GPTQ_API int b200gptq_dense_gemv(const void* x, const void* w, void* y, int rows, int K, int N, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

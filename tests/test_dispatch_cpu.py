@@ -64,3 +64,22 @@ def test_decode_positions_are_checked_on_the_host():
         check_positions(512, 257, 768)
     with pytest.raises(ValueError):
         check_positions(-1, 1, 768)
+
+
+def test_registered_operator_has_a_shape_rule():
+    """torch.ops.b200gptq.quant_matmul is registered with a fake (meta) implementation: tracing tools can infer the
+    output of a QuantLinear without running it (the reference module is not traceable at all: it calls pycuda)."""
+    import torch
+    from autogptq.tvm_b200 import torch_ops  # noqa: F401  (registers the operator)
+    op = torch.ops.b200gptq.quant_matmul
+    K, N, bits = 256, 96, 4
+    x = torch.empty((5, K), dtype=torch.float16, device="meta")
+    qweight = torch.empty((K // 32 * bits, N), dtype=torch.int32, device="meta")
+    qzeros = torch.empty((2, N // 32 * bits), dtype=torch.int32, device="meta")
+    scales = torch.empty((2, N), dtype=torch.float16, device="meta")
+    y = op(x, qweight, qzeros, scales, None, None, None, bits, 128, True)
+    assert y.shape == (5, N) and y.dtype == torch.float16 and y.device.type == "meta"
+    import pytest
+    with pytest.raises(Exception):
+        op(torch.empty((5, K + 32), dtype=torch.float16, device="meta"), qweight, qzeros, scales, None, None, None,
+           bits, 128, True)

@@ -87,3 +87,20 @@ def test_fused_decode_step_matches_the_framework_ops(arch, bits, desc_act):
         va, vb = La.v_cache[:, :, :14].float(), Lb.v_cache[:, :, :14].float()
         assert (ka - kb).abs().max() <= 2e-2 * max(kb.abs().max().item(), 1.0)
         assert (va - vb).abs().max() <= 2e-2 * max(vb.abs().max().item(), 1.0)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 32000), (3, 4096, 4001), (8, 1024, 517), (1, 9216, 50272 // 8)])
+def test_dense_gemv_matches_fp32_product(M, K, N):
+    """Vocabulary projection: fp16 in, fp32 sums of 8-product fp16 partial sums, fp16 out, against the fp64 product."""
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g).half()
+    w = (0.02 * torch.randn(N, K, generator=g)).half()
+    y = ops.dense_gemv(x.to(DEV), w.to(DEV))
+    ref = x.double() @ w.double().t()
+    err = (y.cpu().double() - ref).abs()
+    # one fp16 rounding of the result plus the half-precision partial sums: 2^-10 relative to sum |x w|
+    bound = 2.0 ** -10 * (x.double().abs() @ w.double().abs().t()) + 1e-4
+    assert bool((err <= bound).all()), float((err / bound).max())
+    assert torch.equal(y, ops.dense_gemv(x.to(DEV), w.to(DEV)))
+    with pytest.raises(ValueError):
+        ops.dense_gemv(torch.zeros(9, K, dtype=torch.float16, device=DEV), w.to(DEV))

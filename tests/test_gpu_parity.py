@@ -323,3 +323,26 @@ def test_error_reporting():
         QuantLinear(5, 128, 256, 64, False)
     with pytest.raises(RuntimeError):
         QuantLinear(4, 128, 256, 64, False)(torch.zeros(1, 256))
+
+
+@pytest.mark.parametrize("M", [1, 5, 48])
+def test_traced_forward_equals_eager(M):
+    """torch.compile(fullgraph=True) of a QuantLinear records the registered operator (no graph break, no ctypes
+    call at trace time) and gives the eager result."""
+    import torch._dynamo
+    from autogptq.tvm_b200 import torch_ops  # noqa: F401
+    bits, K, N, gs = 4, 512, 256, 128
+    layer = synth.make_layer(bits, K, N, gs, True, bias=True, seed=3)
+    mod = QuantLinear(bits, gs, K, N, True)
+    mod.qweight, mod.qzeros, mod.scales, mod.g_idx, mod.bias = (layer.qweight, layer.qzeros, layer.scales,
+                                                                  layer.g_idx, layer.bias)
+    mod = mod.to(DEV)
+    x = synth.make_x(M, K, seed=M, device=DEV)
+    want = mod(x)                                   # eager: also builds the run-time layout
+    torch._dynamo.reset()
+    traced = torch.compile(mod, backend="eager", fullgraph=True)
+    got = traced(x)
+    assert torch.equal(got, want)
+    y = torch.ops.b200gptq.quant_matmul(x, mod._qweight_run, mod.qzeros, mod.scales, mod._g_idx_run, mod._x_perm,
+                                        mod.bias, bits, gs, mod._gemm_ok)
+    assert torch.equal(y, want)
