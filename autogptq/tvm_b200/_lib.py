@@ -26,7 +26,9 @@ _SIGNATURES = {
     "b200gptq_workspace_status": (_c_int, [_c_void_p, _c_void_p, _c_void_p]),
     "b200gptq_gemv": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_gemv_tuned": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_void_p]),
+    "b200gptq_gemv_ex": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_void_p]),
     "b200gptq_gemv_plan_create": (_c_int, [_c_void_p] * 7 + [_c_int] * 7),
+    "b200gptq_gemv_plan_create_ex": (_c_int, [_c_void_p] * 7 + [_c_int] * 8),
     "b200gptq_gemv_plan_run": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_gemv_plan_destroy": (None, [_c_void_p]),
     "b200gptq_gemv_path": (_c_int, [_c_int] * 6),
@@ -36,6 +38,8 @@ _SIGNATURES = {
     "b200gptq_tp_buffer_bytes": (_c_size_t, []),
     "b200gptq_gemv_tp": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_void_p,
                                   ctypes.c_longlong, _c_int, _c_int, _c_void_p]),
+    "b200gptq_gemv_tp_ex": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_int, _c_int, _c_void_p,
+                                     ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void_p]),
     "b200gptq_tp_allreduce": (_c_int, [_c_void_p] * 2 + [_c_int] * 4 + [_c_void_p, ctypes.c_longlong, _c_void_p]),
     "b200gptq_tp_status": (_c_int, [_c_void_p, _c_void_p, _c_void_p]),
     "b200gptq_tp_enable_peer": (_c_int, [_c_int]),
@@ -96,6 +100,7 @@ def check(status: int, where: str) -> None:
 
 PATH_STREAM = 1
 PATH_GENERIC = 2
+ACT_NONE, ACT_SWIGLU, ACT_RELU = 0, 1, 2
 
 
 def gemv_path(M: int, K: int, N: int, bits: int, group_size: int, has_g_idx: bool) -> int:

@@ -153,6 +153,22 @@ int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, const int32_t* qz
                         const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
                         int bits, int group_size, void* workspace, size_t workspace_bytes, int slices_per_sm,
                         int ctas_per_sm, void* stream) {
+    return b200gptq_gemv_ex(x, qweight, qzeros, scales, g_idx, x_perm, bias, y, M, K, N, bits, group_size, workspace,
+                            workspace_bytes, slices_per_sm, ctas_per_sm, B200GPTQ_ACT_NONE, stream);
+}
+
+// An input activation is folded into the streaming kernel's read of x only: the general kernel does not have it,
+// and SwiGLU reads two runs of the row, which the gather path's single copy of x does not hold.
+static bool act_supported(int input_act, bool streams, const int32_t* x_perm) {
+    if (input_act == B200GPTQ_ACT_NONE) return true;
+    if (input_act != B200GPTQ_ACT_SWIGLU && input_act != B200GPTQ_ACT_RELU) return false;
+    return streams && !(input_act == B200GPTQ_ACT_SWIGLU && x_perm);
+}
+
+int b200gptq_gemv_ex(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                     const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
+                     int bits, int group_size, void* workspace, size_t workspace_bytes, int slices_per_sm,
+                     int ctas_per_sm, int input_act, void* stream) {
     if (slices_per_sm < 0 || slices_per_sm > 8 || ctas_per_sm < 0 || ctas_per_sm > 4) return B200GPTQ_ERR_SHAPE;
     if (!x || !qweight || !qzeros || !scales || !y) return B200GPTQ_ERR_NULL_POINTER;
     if (int st = check_layer(K, N, bits, &group_size)) return st;
@@ -163,12 +179,14 @@ int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, const int32_t* qz
         return B200GPTQ_ERR_WORKSPACE;
     if (!aligned16(workspace)) return B200GPTQ_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size)) {
-        const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
+    const bool streams = !g_idx && gemv_stream_supported(M, K, N, bits, group_size);
+    if (!act_supported(input_act, streams, x_perm)) return B200GPTQ_ERR_SHAPE;
+    if (streams) {
+        const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, input_act};
         return gemv_stream_dispatch_knobs(static_cast<const __half*>(x), qweight, qzeros,
                                           static_cast<const __half*>(scales), x_perm, static_cast<const __half*>(bias),
                                           static_cast<__half*>(y), M, K, N, bits, group_size, workspace, st,
-                                          (slices_per_sm || ctas_per_sm) ? knobs : nullptr);
+                                          (slices_per_sm || ctas_per_sm || input_act) ? knobs : nullptr);
     }
     return gemv_generic_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
                                  g_idx, x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K, N,
@@ -187,6 +205,14 @@ struct b200gptq_gemv_plan {
 int b200gptq_gemv_plan_create(b200gptq_gemv_plan** out, const int32_t* qweight, const int32_t* qzeros,
                               const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,
                               int M, int K, int N, int bits, int group_size, int slices_per_sm, int ctas_per_sm) {
+    return b200gptq_gemv_plan_create_ex(out, qweight, qzeros, scales, g_idx, x_perm, bias, M, K, N, bits, group_size,
+                                        slices_per_sm, ctas_per_sm, B200GPTQ_ACT_NONE);
+}
+
+int b200gptq_gemv_plan_create_ex(b200gptq_gemv_plan** out, const int32_t* qweight, const int32_t* qzeros,
+                                 const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,
+                                 int M, int K, int N, int bits, int group_size, int slices_per_sm, int ctas_per_sm,
+                                 int input_act) {
     if (!out || !qweight || !qzeros || !scales) return B200GPTQ_ERR_NULL_POINTER;
     *out = nullptr;
     if (int st = check_layer(K, N, bits, &group_size)) return st;
@@ -198,11 +224,13 @@ int b200gptq_gemv_plan_create(b200gptq_gemv_plan** out, const int32_t* qweight, 
     *p = {qweight, qzeros, g_idx, x_perm, static_cast<const __half*>(scales), static_cast<const __half*>(bias),
           M, K, N, bits, group_size, slices_per_sm, ctas_per_sm,
           b200gptq_workspace_bytes(B200GPTQ_OP_GEMV, M, K, N, bits), nullptr};
-    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size)) {
-        const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
+    const bool streams = !g_idx && gemv_stream_supported(M, K, N, bits, group_size);
+    if (!act_supported(input_act, streams, x_perm)) { delete p; return B200GPTQ_ERR_SHAPE; }
+    if (streams) {
+        const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, input_act};
         int st = B200GPTQ_OK;
         p->stream = gemv_stream_plan_create(qweight, p->scales, x_perm != nullptr, M, K, N, bits, group_size,
-                                            (slices_per_sm || ctas_per_sm) ? knobs : nullptr, &st);
+                                            (slices_per_sm || ctas_per_sm || input_act) ? knobs : nullptr, &st);
         if (!p->stream) { delete p; return st; }
     }
     *out = p;

@@ -418,7 +418,19 @@ struct Plan {
                       // the CTA's rows otherwise): 2 into bytes of its own, 1 into the bytes of the partial sums, 0 not
     int early;        // when dependents may be launched: 0 once this CTA has passed its own wait, 1 as soon as it runs,
                       // 2 once all its weights are requested
+    int xact;         // activation applied to x as it is read: 0 none, 1 SwiGLU (x holds [gate | up], 2 K values per
+                      // row), 2 ReLU -- the element-wise kernel between two linears of a decode step folded into the second
 };
+
+// The two activations, rounded exactly like the stand-alone kernel (b200gptq_act): SiLU to fp16, then the product.
+__device__ __forceinline__ unsigned short act_relu(unsigned short h) {
+    return __half_as_ushort(__float2half_rn(fmaxf(__half2float(__ushort_as_half(h)), 0.f)));
+}
+__device__ __forceinline__ unsigned short act_swiglu(unsigned short g, unsigned short u) {
+    const float gf = __half2float(__ushort_as_half(g));
+    const float s = __half2float(__float2half_rn(gf / (1.f + __expf(-gf))));
+    return __half_as_ushort(__float2half_rn(s * __half2float(__ushort_as_half(u))));
+}
 
 template <int BITS> __host__ __device__ constexpr int unit_bytes() { return Traits<BITS>::kWordRows * kRowPitch; }
 // Dynamic shared memory, in this order: ring | xs | s_sm | z_sm | ps | part | red
@@ -584,6 +596,15 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const bool zstr = BITS == 3 && zsh > 29;   // the field straddles two words
 
     const unsigned short* xu = reinterpret_cast<const unsigned short*>(x);
+    // x[m, k] as the products see it (k: row of K after the gather)
+    auto load_x = [&](int m, int k) -> unsigned short {
+        if (plan.xact == 1) {
+            const unsigned short* row = xu + (size_t)m * 2 * K;
+            return act_swiglu(__ldcg(row + k), __ldcg(row + K + k));
+        }
+        const unsigned short h = use_xfull ? xfull[m * xrow_halves + k - xrow_first] : __ldcg(xu + (size_t)m * K + k);
+        return plan.xact == 2 ? act_relu(h) : h;
+    };
 
     int slot = 0, round = 0;
     bool first = true, triggered = false;
@@ -664,13 +685,8 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                     await_x();
                 }
                 unsigned short xv[8];
-                if (use_xfull) {
-    #pragma unroll
-                    for (int i = 0; i < 8; ++i) xv[i] = active ? xfull[m * xrow_halves + kx[i] - xrow_first] : (unsigned short)0;
-                } else {
-    #pragma unroll
-                    for (int i = 0; i < 8; ++i) xv[i] = active ? __ldcg(xu + (size_t)m * K + kx[i]) : (unsigned short)0;
-                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xv[i] = active ? load_x(m, kx[i]) : (unsigned short)0;
                 float sx = 0.f, scx = 0.f;
     #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -720,7 +736,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     unsigned short h = 0;
-                    if (active) h = use_xfull ? xfull[kx[i] - xrow_first] : __ldcg(xu + kx[i]);
+                    if (active) h = load_x(0, kx[i]);
                     xf[i] = __half2float(__ushort_as_half(h));
                     mx = max(mx, __float_as_uint(fabsf(xf[i])));
                 }
@@ -984,7 +1000,8 @@ int max_groups_per_stage(const Plan& p, int group_size) {
 
 // knobs (all optional, 0 = the default): [0] CTAs of one grid per SM that the cluster size is chosen for,
 // [1] CTAs per SM that the shared-memory footprint is sized for, [2] cap on ring units, [3] trigger of dependents
-// (1 after the own wait, 2 at entry, 3 once all weights are requested), [4] 1 = gather x from global memory
+// (1 after the own wait, 2 at entry, 3 once all weights are requested), [4] 1 = gather x from global memory,
+// [5] activation applied to x as it is read (Plan::xact)
 template <int BITS>
 Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* knobs, int* smem_bytes) {
     Plan p;
@@ -1004,12 +1021,14 @@ Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* kn
     p.group_box = max_groups_per_stage(p, group_size);
     p.push = (c > 1 && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
     p.early = (knobs && knobs[3] > 0) ? knobs[3] - 1 : 0;
+    p.xact = knobs ? knobs[5] : 0;
     // layers with a gather take x through a linear bulk copy when it is small enough (knobs[4] == 1 switches it
     // off): small copies get bytes of their own, larger ones share the bytes of the partial sums (the CTA then joins
     // its cluster's barrier only when it has finished with x).  Without a gather a CTA reads only its own rows of x,
     // and plain loads measured faster than the copy.
     const int xcopy_bytes = M * (has_perm ? K : longest * kUnitRows) * 2;
     p.xfull = (!has_perm || (knobs && knobs[4] == 1)) ? 0 : (xcopy_bytes <= 4096 ? 2 : (xcopy_bytes <= kXFullMax ? 1 : 0));
+    if (p.xact == 1) p.xfull = 0;   // gate and up are two runs of the row: no single copy (callers fuse SwiGLU only without a gather)
     int tail = part_bytes(M) + (p.push ? red_bytes(M, c) : 0);
     if (p.xfull == 2) tail += xcopy_bytes;
     if (p.xfull == 1 && tail < xcopy_bytes) tail = xcopy_bytes;

@@ -95,8 +95,20 @@ int b200gptq_gemv_tp(const void* x, const int32_t* qweight, const int32_t* qzero
                      int bits, int group_size, void* workspace, size_t workspace_bytes, int rank, int world,
                      void* const* peer_buffers, long long timeout_cycles, int slices_per_sm, int ctas_per_sm,
                      void* stream) {
+    return b200gptq_gemv_tp_ex(x, qweight, qzeros, scales, g_idx, x_perm, bias, y, M, K, N, bits, group_size, workspace,
+                               workspace_bytes, rank, world, peer_buffers, timeout_cycles, slices_per_sm, ctas_per_sm,
+                               B200GPTQ_ACT_NONE, stream);
+}
+
+int b200gptq_gemv_tp_ex(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                        const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y, int M, int K, int N,
+                        int bits, int group_size, void* workspace, size_t workspace_bytes, int rank, int world,
+                        void* const* peer_buffers, long long timeout_cycles, int slices_per_sm, int ctas_per_sm,
+                        int input_act, void* stream) {
     if (slices_per_sm < 0 || slices_per_sm > 8 || ctas_per_sm < 0 || ctas_per_sm > 4) return B200GPTQ_ERR_SHAPE;
-    const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, 0};
+    if (input_act != B200GPTQ_ACT_NONE && input_act != B200GPTQ_ACT_SWIGLU && input_act != B200GPTQ_ACT_RELU)
+        return B200GPTQ_ERR_SHAPE;
+    const int knobs[6] = {slices_per_sm, ctas_per_sm, 0, 0, 0, input_act};
     if (!x || !qweight || !qzeros || !scales || !y) return B200GPTQ_ERR_NULL_POINTER;
     if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return B200GPTQ_ERR_BITS;
     if (K <= 0 || N <= 0 || K % 32 != 0 || N % 32 != 0 || M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
@@ -109,10 +121,13 @@ int b200gptq_gemv_tp(const void* x, const int32_t* qweight, const int32_t* qzero
     TpArgs tp;
     if (int st = fill_tp(&tp, rank, world, peer_buffers, timeout_cycles)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (!g_idx && gemv_stream_supported(M, K, N, bits, group_size))
+    const bool streams = !g_idx && gemv_stream_supported(M, K, N, bits, group_size);
+    // the activation is part of the streaming kernel's read of x only (and SwiGLU not together with a gather)
+    if (input_act != B200GPTQ_ACT_NONE && (!streams || (input_act == B200GPTQ_ACT_SWIGLU && x_perm))) return B200GPTQ_ERR_SHAPE;
+    if (streams)
         return gemv_stream_dispatch_tp(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),
                                        x_perm, static_cast<const __half*>(bias), static_cast<__half*>(y), M, K, N, bits,
-                                       group_size, workspace, s, (slices_per_sm || ctas_per_sm) ? knobs : nullptr,
+                                       group_size, workspace, s, (slices_per_sm || ctas_per_sm || input_act) ? knobs : nullptr,
                                        world > 1 ? &tp : nullptr);
     // general kernel: this rank's sums first (without the bias), then the exchange as a kernel of its own
     if (int st = gemv_generic_dispatch(static_cast<const __half*>(x), qweight, qzeros, static_cast<const __half*>(scales),

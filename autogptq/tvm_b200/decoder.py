@@ -28,7 +28,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import ops, synth, tp
+from . import _lib, ops, synth, tp
 from .qlinear import QuantLinear
 
 
@@ -159,10 +159,12 @@ class GPTQDecoder:
     """Batch of sequences, one token per step after the prompt; greedy sampling."""
 
     def __init__(self, cfg: DecoderConfig, batch: int = 1, device="cuda", group=None, fused: bool = True,
-                 single: bool = False, fused_allreduce: bool = False):
+                 single: bool = False, fused_allreduce: bool = False, fold_activation: bool = True):
         """``single=True`` builds the whole model on this device even inside a process group (the unsharded
-        yardstick of a tensor-parallel run)."""
+        yardstick of a tensor-parallel run).  ``fold_activation``: decode steps of up to 8 sequences let the second
+        FFN linear apply SiLU(gate) * up / ReLU as it reads its input instead of launching the element-wise kernel."""
         self.cfg, self.batch = cfg, batch
+        self.fold_activation = fold_activation
         self.fused = fused and cfg.head_dim in (64, 128)   # decode steps use the fused helper kernels
         self.device = torch.device(device)
         self.group = group
@@ -227,13 +229,15 @@ class GPTQDecoder:
             dist.all_reduce(t, group=self.group)
         return t
 
-    def _row(self, mod: QuantLinear, x):
-        """A row-parallel linear: this rank's slice of the input in, the sum over ranks out."""
+    def _row(self, mod: QuantLinear, x, input_act: int = 0):
+        """A row-parallel linear: this rank's slice of the input in, the sum over ranks out.  ``input_act``: the
+        activation in front of it, folded into the layer's read of ``x`` (the caller has checked ``mod.can_fold``)."""
         if self.world == 1:
-            return mod(x)
+            return mod.forward_act(x, input_act) if input_act else mod(x)
         if self.exchange is not None:
-            return mod.forward_reduce(x)
-        return self._all_reduce(mod(x))          # the shard of rank 0 carries the bias
+            return mod.forward_reduce(x, input_act)
+        y = mod.forward_act(x, input_act) if input_act else mod(x)
+        return self._all_reduce(y)               # the shard of rank 0 carries the bias
 
     def _rope(self, t, cos, sin):
         # t: [B, H, S, hd]; cos/sin: [S, hd/2]
@@ -364,9 +368,13 @@ class GPTQDecoder:
             o = self._row(L.o, att)
             ops.add_norm(x, o, L.norm2_w, L.norm2_b, h, eps, rms)
             u = L.up(h)
-            a = torch.empty((B, L.inter_local), dtype=torch.float16, device=self.device)
-            ops.act(u, a, L.inter_local, rms)
-            delta = self._row(L.down, a)
+            fold = _lib.ACT_SWIGLU if rms else _lib.ACT_RELU
+            if self.fold_activation and isinstance(L.down, QuantLinear) and L.down.can_fold(B, fold):
+                delta = self._row(L.down, u, fold)       # SiLU(gate) * up / ReLU inside the GEMV's read of x
+            else:
+                a = torch.empty((B, L.inter_local), dtype=torch.float16, device=self.device)
+                ops.act(u, a, L.inter_local, rms)
+                delta = self._row(L.down, a)
         ops.add_norm(x, delta, self.final_norm_w, self.final_norm_b, h, eps, rms)
         self.last_hidden = h
         logits = self._project(h)

@@ -123,7 +123,7 @@ def sort_rows(qweight, g_idx, bits: int):
 
 
 def _matmul(fn_name: str, op: int, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits, group_size,
-            out, workspace, tuning=None):
+            out, workspace, tuning=None, input_act: int = 0):
     _need_cuda("x", x, torch.float16)
     _need_cuda("qweight", qweight, torch.int32)
     _need_cuda("qzeros", qzeros, torch.int32)
@@ -135,8 +135,9 @@ def _matmul(fn_name: str, op: int, x, qweight, qzeros, scales, g_idx, x_perm, bi
     if bias is not None:
         _need_cuda("bias", bias, torch.float16)
     K, N = layer_dims(qweight, bits)
-    if x.dim() != 2 or x.shape[1] != K:
-        raise ValueError(f"x must be [M, {K}], got {tuple(x.shape)}")
+    xk = 2 * K if input_act == _lib.ACT_SWIGLU else K
+    if x.dim() != 2 or x.shape[1] != xk:
+        raise ValueError(f"x must be [M, {xk}], got {tuple(x.shape)}")
     M = x.shape[0]
     dev = x.device
     if out is None:
@@ -149,12 +150,13 @@ def _matmul(fn_name: str, op: int, x, qweight, qzeros, scales, g_idx, x_perm, bi
     if workspace is None:
         workspace = get_workspace(dev, need)
     with torch.cuda.device(dev):
-        if tuning is not None:
-            fn_name = "b200gptq_gemv_tuned"
-            st = _lib.lib.b200gptq_gemv_tuned(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
-                                              _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
-                                              _ptr(workspace), workspace.numel() * workspace.element_size(),
-                                              int(tuning[0]), int(tuning[1]), _stream(dev))
+        if tuning is not None or input_act:
+            fn_name = "b200gptq_gemv_ex"
+            st = _lib.lib.b200gptq_gemv_ex(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
+                                           _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
+                                           _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                           int(tuning[0]) if tuning else 0, int(tuning[1]) if tuning else 0,
+                                           int(input_act), _stream(dev))
         else:
             st = getattr(_lib.lib, fn_name)(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
                                             _ptr(x_perm), _ptr(bias), _ptr(out), M, K, N, bits, group_size,
@@ -165,11 +167,23 @@ def _matmul(fn_name: str, op: int, x, qweight, qzeros, scales, g_idx, x_perm, bi
 
 
 def gemv(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None,
-         out=None, workspace=None, tuning=None):
-    """Decode GEMV, ``x`` fp16 ``[M<=8, K]`` -> fp16 ``[M, N]``.  ``tuning = (slices_per_sm, ctas_per_sm)`` selects
-    ``b200gptq_gemv_tuned`` (see the header for the two parameters); ``None`` means the library defaults."""
+         out=None, workspace=None, tuning=None, input_act: int = 0):
+    """Decode GEMV, ``x`` fp16 ``[M<=8, K]`` -> fp16 ``[M, N]``.  ``tuning = (slices_per_sm, ctas_per_sm)`` and
+    ``input_act`` (``_lib.ACT_SWIGLU``: ``x`` is ``[M, 2K] = [gate | up]``; ``_lib.ACT_RELU``) select
+    ``b200gptq_gemv_ex`` (see the header); the defaults mean the plain call.  Raises when the activation cannot be
+    folded for this layer (see :func:`can_fold_act`)."""
     return _matmul("b200gptq_gemv", _lib.OP_GEMV, x, qweight, qzeros, scales, g_idx, x_perm, bias, bits,
-                   group_size, out, workspace, tuning)
+                   group_size, out, workspace, tuning, input_act)
+
+
+def can_fold_act(M: int, K: int, N: int, bits: int, group_size: int, has_g_idx: bool, has_perm: bool, input_act: int) -> bool:
+    """Whether ``b200gptq_gemv_ex`` folds ``input_act`` into this GEMV (only the streaming kernel does, and SwiGLU not
+    together with a gather); otherwise the caller runs :func:`act` first."""
+    if not input_act:
+        return True
+    if _lib.gemv_path(M, K, N, bits, group_size, has_g_idx) != _lib.PATH_STREAM:
+        return False
+    return not (input_act == _lib.ACT_SWIGLU and has_perm)
 
 
 def gemm(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, bias=None, x_perm=None,
@@ -183,7 +197,8 @@ class GemvPlan:
     """A prepared decode GEMV for one layer and one row count (``b200gptq_gemv_plan_*``): kernel choice, work split
     and TMA descriptors are built once, a call is one kernel launch.  Keeps the layer's tensors alive."""
 
-    def __init__(self, qweight, qzeros, scales, g_idx, x_perm, bias, M: int, bits: int, group_size: int, tuning=None):
+    def __init__(self, qweight, qzeros, scales, g_idx, x_perm, bias, M: int, bits: int, group_size: int, tuning=None,
+                 input_act: int = 0):
         _need_cuda("qweight", qweight, torch.int32)
         _need_cuda("qzeros", qzeros, torch.int32)
         _need_cuda("scales", scales, torch.float16)
@@ -196,16 +211,18 @@ class GemvPlan:
         self.device = qweight.device
         import ctypes
         handle = ctypes.c_void_p(0)
-        st = _lib.lib.b200gptq_gemv_plan_create(ctypes.byref(handle), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx),
-                                                _ptr(x_perm), _ptr(bias), M, self.K, self.N, bits, group_size,
-                                                int(tuning[0]) if tuning else 0, int(tuning[1]) if tuning else 0)
-        _lib.check(st, "b200gptq_gemv_plan_create")
+        self.xk = 2 * self.K if input_act == _lib.ACT_SWIGLU else self.K
+        st = _lib.lib.b200gptq_gemv_plan_create_ex(ctypes.byref(handle), _ptr(qweight), _ptr(qzeros), _ptr(scales),
+                                                   _ptr(g_idx), _ptr(x_perm), _ptr(bias), M, self.K, self.N, bits,
+                                                   group_size, int(tuning[0]) if tuning else 0,
+                                                   int(tuning[1]) if tuning else 0, int(input_act))
+        _lib.check(st, "b200gptq_gemv_plan_create_ex")
         self._handle = handle
         self._need = _lib.workspace_bytes(_lib.OP_GEMV, M, self.K, self.N, bits)
 
     def run(self, x, out=None):
-        if not x.is_cuda or x.dtype != torch.float16 or not x.is_contiguous() or tuple(x.shape) != (self.M, self.K):
-            raise ValueError(f"x must be a contiguous fp16 CUDA tensor [{self.M}, {self.K}]")
+        if not x.is_cuda or x.dtype != torch.float16 or not x.is_contiguous() or tuple(x.shape) != (self.M, self.xk):
+            raise ValueError(f"x must be a contiguous fp16 CUDA tensor [{self.M}, {self.xk}]")
         if out is None:
             out = torch.empty((self.M, self.N), dtype=torch.float16, device=x.device)
         ws = get_workspace(x.device, self._need)      # one buffer per (device, stream)
@@ -222,7 +239,7 @@ class GemvPlan:
 
 
 def gemv_tp(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, exchange, bias=None, x_perm=None,
-            out=None, workspace=None, tuning=None):
+            out=None, workspace=None, tuning=None, input_act: int = 0):
     """Row-parallel decode GEMV with the sum over ranks fused in (``b200gptq_gemv_tp``): ``x`` is this rank's slice of
     the input ``[M<=8, K_local]``, the packed buffers are this rank's shard, ``bias`` is the full bias (the same on
     every rank).  ``exchange`` is a :class:`exchange.PeerExchange`.  Returns the complete result on every rank."""
@@ -234,8 +251,9 @@ def gemv_tp(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, excha
         if t is not None:
             _need_cuda(name, t, dt)
     K, N = layer_dims(qweight, bits)
-    if x.dim() != 2 or x.shape[1] != K:
-        raise ValueError(f"x must be [M, {K}], got {tuple(x.shape)}")
+    xk = 2 * K if input_act == _lib.ACT_SWIGLU else K
+    if x.dim() != 2 or x.shape[1] != xk:
+        raise ValueError(f"x must be [M, {xk}], got {tuple(x.shape)}")
     M = x.shape[0]
     dev = x.device
     if out is None:
@@ -243,12 +261,13 @@ def gemv_tp(x, qweight, qzeros, scales, g_idx, bits: int, group_size: int, excha
     if workspace is None:
         workspace = get_workspace(dev, _lib.workspace_bytes(_lib.OP_GEMV, M, K, N, bits))
     with torch.cuda.device(dev):
-        st = _lib.lib.b200gptq_gemv_tp(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), _ptr(x_perm),
-                                       _ptr(bias), _ptr(out), M, K, N, bits, group_size, _ptr(workspace),
-                                       workspace.numel() * workspace.element_size(), exchange.rank, exchange.world,
-                                       exchange.peer_table, exchange.timeout_cycles,
-                                       int(tuning[0]) if tuning else 0, int(tuning[1]) if tuning else 0, _stream(dev))
-    _lib.check(st, "b200gptq_gemv_tp")
+        st = _lib.lib.b200gptq_gemv_tp_ex(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), _ptr(x_perm),
+                                          _ptr(bias), _ptr(out), M, K, N, bits, group_size, _ptr(workspace),
+                                          workspace.numel() * workspace.element_size(), exchange.rank, exchange.world,
+                                          exchange.peer_table, exchange.timeout_cycles,
+                                          int(tuning[0]) if tuning else 0, int(tuning[1]) if tuning else 0,
+                                          int(input_act), _stream(dev))
+    _lib.check(st, "b200gptq_gemv_tp_ex")
     return out
 
 

@@ -219,7 +219,35 @@ class QuantLinear(nn.Module):
                 ops.gemv(x2[m0:m0 + GEMV_MAX_M], *args, out=y[m0:m0 + GEMV_MAX_M], **kw)
         return y.reshape(out_shape)
 
-    def forward_reduce(self, x):
+    # ---- the element-wise kernel in front of this layer folded into its read of x (decode batches only) ----
+    def can_fold(self, rows: int, input_act: int) -> bool:
+        """Whether :meth:`forward_act` / ``forward_reduce(..., input_act)`` can take the activation for ``rows`` rows."""
+        if not self._ready():
+            self.post_init()
+        return rows <= GEMV_MAX_M and ops.can_fold_act(rows, self.infeatures, self.outfeatures, self.bits, self.groupsize,
+                                                       self._g_idx_run is not None, self._x_perm is not None, input_act)
+
+    def forward_act(self, u, input_act: int):
+        """``forward(act(u))`` in one launch for up to 8 rows: ``input_act = _lib.ACT_SWIGLU`` (``u`` is
+        ``[..., 2 * in] = [gate | up]``) or ``_lib.ACT_RELU`` (``b200gptq_gemv_plan_create_ex``).  The caller checks
+        :meth:`can_fold` first."""
+        if not self._ready():
+            self.post_init()
+        u2 = u.half().reshape(-1, u.shape[-1])
+        if not u2.is_contiguous():
+            u2 = u2.contiguous()
+        M = u2.shape[0]
+        key = (M, self.gemv_tuning, input_act)
+        plan = self._plans.get(key)
+        if plan is None or plan._keep[5] is not self.bias:
+            plan = self._plans[key] = ops.GemvPlan(self._qweight_run, self.qzeros, self.scales, self._g_idx_run,
+                                                 self._x_perm, self.bias, M, self.bits, self.groupsize,
+                                                 self.gemv_tuning, input_act)
+        with torch.cuda.device(u2.device):
+            y = plan.run(u2)
+        return y.reshape(u.shape[:-1] + (self.outfeatures,))
+
+    def forward_reduce(self, x, input_act: int = 0):
         """Row-parallel forward: this rank's slice of the input in, the complete output (summed over ranks) out.
         Up to 8 rows go through ``b200gptq_gemv_tp`` (sum fused into the kernel, peer memory); more rows use the
         process group's all-reduce."""
@@ -232,8 +260,11 @@ class QuantLinear(nn.Module):
             x2 = x2.contiguous()
         if x2.shape[0] <= GEMV_MAX_M:
             y = ops.gemv_tp(x2, self._qweight_run, self.qzeros, self.scales, self._g_idx_run, self.bits, self.groupsize,
-                            self.exchange, bias=self.tp_bias, x_perm=self._x_perm, tuning=self.gemv_tuning)
+                            self.exchange, bias=self.tp_bias, x_perm=self._x_perm, tuning=self.gemv_tuning,
+                            input_act=input_act)
         else:
+            if input_act:
+                raise ValueError("an input activation is folded for up to 8 rows only")
             import torch.distributed as dist
             saved, self.bias = self.bias, None
             try:

@@ -133,6 +133,27 @@ B200GPTQ_API int b200gptq_gemv_tuned(const void* x, const int32_t* qweight, cons
                         int slices_per_sm, int ctas_per_sm, void* stream);
 
 /*
+ * The GEMV with an activation folded into its read of x, so that the element-wise kernel between two linears of
+ * a decode step (SiLU(gate) * up before `down_proj`, ReLU before `fc2`: auto_gptq/modeling/llama.py:8-12,
+ * opt.py:11-16 name the layer pairs) is not a launch of its own:
+ *   B200GPTQ_ACT_SWIGLU   x is [M, 2 K] = [gate | up]; the products see fp16(fp16(silu(gate)) * up), rounded exactly like
+ *                         b200gptq_act.  Not together with x_perm.
+ *   B200GPTQ_ACT_RELU     x is [M, K]; the products see max(x, 0).
+ * Only the streaming kernel has it: a call that the general kernel would serve (non-NULL g_idx, 2/8 bits, ...)
+ * returns B200GPTQ_ERR_SHAPE and the caller runs b200gptq_act first.  Otherwise as b200gptq_gemv_tuned
+ * (B200GPTQ_ACT_NONE gives exactly that); b200gptq_gemv_plan_create_ex and b200gptq_gemv_tp_ex are the plan and
+ * the tensor-parallel form.
+ */
+#define B200GPTQ_ACT_NONE 0
+#define B200GPTQ_ACT_SWIGLU 1
+#define B200GPTQ_ACT_RELU 2
+B200GPTQ_API int b200gptq_gemv_ex(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                     const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
+                     int M, int K, int N, int bits, int group_size,
+                     void* workspace, size_t workspace_bytes,
+                     int slices_per_sm, int ctas_per_sm, int input_act, void* stream);
+
+/*
  * The same GEMV as a plan: what can be decided before x is known (kernel choice, work split, the TMA
  * descriptors of the layer's qweight and scales) is built once per (layer, M) and kept in an opaque HOST
  * object, so that a call costs one kernel launch.  This is the counterpart of the reference's per-shape
@@ -145,6 +166,10 @@ typedef struct b200gptq_gemv_plan b200gptq_gemv_plan;
 B200GPTQ_API int b200gptq_gemv_plan_create(b200gptq_gemv_plan** out, const int32_t* qweight, const int32_t* qzeros,
                               const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,
                               int M, int K, int N, int bits, int group_size, int slices_per_sm, int ctas_per_sm);
+B200GPTQ_API int b200gptq_gemv_plan_create_ex(b200gptq_gemv_plan** out, const int32_t* qweight, const int32_t* qzeros,
+                              const void* scales, const int32_t* g_idx, const int32_t* x_perm, const void* bias,
+                              int M, int K, int N, int bits, int group_size, int slices_per_sm, int ctas_per_sm,
+                              int input_act);
 B200GPTQ_API int b200gptq_gemv_plan_run(const b200gptq_gemv_plan* plan, const void* x, void* y,
                            void* workspace, size_t workspace_bytes, void* stream);
 B200GPTQ_API void b200gptq_gemv_plan_destroy(b200gptq_gemv_plan* plan);
@@ -270,6 +295,13 @@ B200GPTQ_API int b200gptq_gemv_tp(const void* x, const int32_t* qweight, const i
                      void* workspace, size_t workspace_bytes,
                      int rank, int world, void* const* peer_buffers, long long timeout_cycles,
                      int slices_per_sm, int ctas_per_sm, void* stream);
+/* b200gptq_gemv_tp with the input activation of b200gptq_gemv_ex (x is this rank's slice: [M, 2 K_local] for SwiGLU). */
+B200GPTQ_API int b200gptq_gemv_tp_ex(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                     const int32_t* g_idx, const int32_t* x_perm, const void* bias, void* y,
+                     int M, int K, int N, int bits, int group_size,
+                     void* workspace, size_t workspace_bytes,
+                     int rank, int world, void* const* peer_buffers, long long timeout_cycles,
+                     int slices_per_sm, int ctas_per_sm, int input_act, void* stream);
 B200GPTQ_API int b200gptq_tp_allreduce(void* y, const void* bias, int M, int N, int rank, int world,
                           void* const* peer_buffers, long long timeout_cycles, void* stream);
 B200GPTQ_API int b200gptq_tp_status(const void* own_buffer, void* stream, unsigned int* host_out);

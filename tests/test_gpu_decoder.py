@@ -104,3 +104,23 @@ def test_dense_gemv_matches_fp32_product(M, K, N):
     assert torch.equal(y, ops.dense_gemv(x.to(DEV), w.to(DEV)))
     with pytest.raises(ValueError):
         ops.dense_gemv(torch.zeros(9, K, dtype=torch.float16, device=DEV), w.to(DEV))
+
+
+@pytest.mark.parametrize("arch,bits,desc_act,batch", [("llama", 4, False, 1), ("opt", 3, True, 1), ("llama", 4, False, 4)])
+def test_folded_activation_gives_the_same_tokens(arch, bits, desc_act, batch):
+    """The second FFN linear applying SiLU(gate) * up / ReLU as it reads its input (one launch fewer per layer) is
+    bit-identical to the separate element-wise kernel: same logits, same tokens."""
+    cfg = _small(arch, bits, desc_act)
+    prompt = torch.randint(0, cfg.vocab, (batch, 9), generator=torch.Generator().manual_seed(3)).to(DEV)
+    outs = []
+    for fold in (True, False):
+        m = decoder.GPTQDecoder(cfg, batch=batch, device=DEV, fold_activation=fold)
+        m.prefill(prompt)
+        m.capture()
+        toks = m.decode(5).cpu()
+        outs.append((toks, m.last_logits.cpu()))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
+    m = decoder.GPTQDecoder(cfg, batch=batch, device=DEV)
+    folds = [L.down.can_fold(batch, 1 if arch == "llama" else 2) for L in m.layers]
+    assert all(folds), "the miniature's FFN layers are expected to take the folded activation"

@@ -346,3 +346,36 @@ def test_traced_forward_equals_eager(M):
     y = torch.ops.b200gptq.quant_matmul(x, mod._qweight_run, mod.qzeros, mod.scales, mod._g_idx_run, mod._x_perm,
                                         mod.bias, bits, gs, mod._gemm_ok)
     assert torch.equal(y, want)
+
+
+@pytest.mark.parametrize("bits,K,N,act_order", [(4, 11008, 4096, False), (3, 4096, 1056, False), (3, 4096, 1024, True),
+                                                (4, 1024, 512, True)])
+@pytest.mark.parametrize("M", [1, 4])
+@pytest.mark.parametrize("kind", ["swiglu", "relu"])
+def test_gemv_with_folded_activation(bits, K, N, act_order, M, kind):
+    """b200gptq_gemv_ex / plan_create_ex: the activation applied inside the GEMV's read of x gives bit for bit what
+    b200gptq_act followed by the plain GEMV gives (both fp16 paths and the integer path, with and without a gather)."""
+    input_act = _lib.ACT_SWIGLU if kind == "swiglu" else _lib.ACT_RELU
+    layer = synth.make_layer(bits, K, N, 128, act_order, bias=True, seed=K + N).to(DEV)
+    if act_order:
+        qw, perm, _ = ops.sort_rows(layer.qweight, layer.g_idx, bits)
+    else:
+        qw, perm = layer.qweight, None
+    width = 2 * K if kind == "swiglu" else K
+    u = synth.make_x(M, width, seed=M + 7, device=DEV)
+    foldable = ops.can_fold_act(M, K, N, bits, 128, False, perm is not None, input_act)
+    assert foldable == (not (kind == "swiglu" and act_order))
+    if not foldable:
+        with pytest.raises(ValueError):
+            ops.gemv(u, qw, layer.qzeros, layer.scales, None, bits, 128, bias=layer.bias, x_perm=perm, input_act=input_act)
+        return
+    a = torch.empty((M, K), dtype=torch.float16, device=DEV)
+    ops.act(u, a, K, kind == "swiglu")
+    want = ops.gemv(a, qw, layer.qzeros, layer.scales, None, bits, 128, bias=layer.bias, x_perm=perm)
+    got = ops.gemv(u, qw, layer.qzeros, layer.scales, None, bits, 128, bias=layer.bias, x_perm=perm, input_act=input_act)
+    assert torch.equal(got, want)
+    plan = ops.GemvPlan(qw, layer.qzeros, layer.scales, None, perm, layer.bias, M, bits, 128, None, input_act)
+    assert torch.equal(plan.run(u), want)
+    # the general kernel has no folded activation: asking for it is refused, not ignored
+    with pytest.raises(ValueError):
+        ops.gemv(u, layer.qweight, layer.qzeros, layer.scales, layer.g_idx, bits, 128, input_act=input_act)
