@@ -121,6 +121,6 @@ def test_folded_activation_gives_the_same_tokens(arch, bits, desc_act, batch):
         outs.append((toks, m.last_logits.cpu()))
     assert torch.equal(outs[0][0], outs[1][0])
     assert torch.equal(outs[0][1], outs[1][1])
-    m = decoder.GPTQDecoder(cfg, batch=batch, device=DEV)
+    m = decoder.GPTQDecoder(cfg, batch=batch, device=DEV, fold_activation=True)
     folds = [L.down.can_fold(batch, 1 if arch == "llama" else 2) for L in m.layers]
     assert all(folds), "the miniature's FFN layers are expected to take the folded activation"
