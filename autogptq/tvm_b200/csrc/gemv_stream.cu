@@ -478,7 +478,9 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local_ptr, uint32_t
 // MULTI = false is the single-row instantiation (M == 1, the decode case that is timed): every loop over the
 // rows of x folds away and the CTA is small enough for three per SM.
 // PERM = false is the instantiation for layers whose x needs no gather (x_perm == NULL).
-template <int BITS, bool MULTI, bool PERM>
+// XACT: the activation applied to x as it is read (Plan::xact), a template parameter because a run-time test per
+// element of x on the path between the dependency wait and the first product costs 3 % of a decode step.
+template <int BITS, bool MULTI, bool PERM, int XACT>
 __global__ void __launch_bounds__(kThreads, MULTI ? 2 : 3)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
                    const __half* x, const int32_t* __restrict__ qzeros, const int32_t* __restrict__ x_perm,
@@ -598,12 +600,13 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const unsigned short* xu = reinterpret_cast<const unsigned short*>(x);
     // x[m, k] as the products see it (k: row of K after the gather)
     auto load_x = [&](int m, int k) -> unsigned short {
-        if (plan.xact == 1) {
+        if constexpr (XACT == 1) {
             const unsigned short* row = xu + (size_t)m * 2 * K;
             return act_swiglu(__ldcg(row + k), __ldcg(row + K + k));
+        } else {
+            const unsigned short h = use_xfull ? xfull[m * xrow_halves + k - xrow_first] : __ldcg(xu + (size_t)m * K + k);
+            return XACT == 2 ? act_relu(h) : h;
         }
-        const unsigned short h = use_xfull ? xfull[m * xrow_halves + k - xrow_first] : __ldcg(xu + (size_t)m * K + k);
-        return plan.xact == 2 ? act_relu(h) : h;
     };
 
     int slot = 0, round = 0;
@@ -1053,6 +1056,19 @@ Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* kn
     return p;
 }
 
+// The instantiation for (several rows of x, gather, activation); SwiGLU is not built together with a gather.
+template <int BITS>
+const void* kernel_for(bool multi, bool perm, int xact) {
+#define B200GPTQ_K(MU, PE, XA) reinterpret_cast<const void*>(gemv_stream_kernel<BITS, MU, PE, XA>)
+    if (xact == 0) return multi ? (perm ? B200GPTQ_K(true, true, 0) : B200GPTQ_K(true, false, 0))
+                                : (perm ? B200GPTQ_K(false, true, 0) : B200GPTQ_K(false, false, 0));
+    if (xact == 2) return multi ? (perm ? B200GPTQ_K(true, true, 2) : B200GPTQ_K(true, false, 2))
+                                : (perm ? B200GPTQ_K(false, true, 2) : B200GPTQ_K(false, false, 2));
+    if (xact == 1 && !perm) return multi ? B200GPTQ_K(true, false, 1) : B200GPTQ_K(false, false, 1);
+    return nullptr;
+#undef B200GPTQ_K
+}
+
 template <int BITS>
 int set_smem_attr_once() {
     static std::once_flag once[64];
@@ -1065,10 +1081,10 @@ int set_smem_attr_once() {
         auto set = [&](const void* f) {
             if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         };
-        set(reinterpret_cast<const void*>(gemv_stream_kernel<BITS, false, false>));
-        set(reinterpret_cast<const void*>(gemv_stream_kernel<BITS, false, true>));
-        set(reinterpret_cast<const void*>(gemv_stream_kernel<BITS, true, false>));
-        set(reinterpret_cast<const void*>(gemv_stream_kernel<BITS, true, true>));
+        for (int multi = 0; multi < 2; ++multi)
+            for (int perm = 0; perm < 2; ++perm)
+                for (int xact = 0; xact < 3; ++xact)
+                    if (const void* f = kernel_for<BITS>(multi != 0, perm != 0, xact)) set(f);
         result[dev] = (int)e;
     });
     if (result[dev] != 0) { set_last_cuda_error(result[dev]); return B200GPTQ_ERR_CUDA; }
@@ -1115,10 +1131,8 @@ int prepare_stream(PreparedStream* ps, const int32_t* qweight, const __half* sca
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
     }
-    ps->kernel = M == 1 ? (has_perm ? (const void*)gemv_stream_kernel<BITS, false, true>
-                                    : (const void*)gemv_stream_kernel<BITS, false, false>)
-                        : (has_perm ? (const void*)gemv_stream_kernel<BITS, true, true>
-                                    : (const void*)gemv_stream_kernel<BITS, true, false>);
+    ps->kernel = kernel_for<BITS>(M != 1, has_perm, ps->plan.xact);
+    if (!ps->kernel) return B200GPTQ_ERR_SHAPE;   // SwiGLU together with a gather: not instantiated
     return B200GPTQ_OK;
 }
 
