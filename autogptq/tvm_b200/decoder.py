@@ -60,24 +60,6 @@ OPT_66B = DecoderConfig(arch="opt", layers=64, hidden=9216, heads=72, inter=3686
                         group_size=128, desc_act=True, max_seq=256)
 
 
-def graph_kernels(dot_path: str) -> dict:
-    """Kernel nodes of a captured decode step by function name (from the DOT dump of the CUDA graph): what one token
-    launches, and the evidence that no library collective is among them."""
-    import re
-    counts: dict = {}
-    with open(dot_path) as f:
-        text = f.read()
-    for label in re.findall(r'label="([^"]*)"', text):
-        if "KERNEL" not in label.upper():
-            continue
-        fields = [t.strip() for t in re.split(r"[|{}]|\\[nl]", label) if t.strip()]
-        names = [t for t in fields if re.search(r"[A-Za-z_]\w*(::|<|_kernel|Kernel)", t) or "(" in t]
-        name = max(names, key=len) if names else (fields[-1] if fields else "?")
-        name = re.sub(r"\(.*", "", name).strip()
-        counts[name] = counts.get(name, 0) + 1
-    return counts
-
-
 def check_positions(pos: int, steps: int, max_seq: int) -> None:
     """Refuse a run that would step past the KV caches: the kernels take the position from device memory (so that a
     captured graph can advance it), which leaves this host-side check as the place where a bad request is reported."""
@@ -383,9 +365,8 @@ class GPTQDecoder:
         self.tokens.copy_(self._pick(logits))
         self.pos.add_(1)
 
-    def capture(self, dot_path: Optional[str] = None):
-        """Warm up (allocates scratch, builds run-time views) and capture one decode step in a CUDA graph.
-        ``dot_path``: also write the captured graph in DOT form there (``graph_kernels`` reads it back)."""
+    def capture(self):
+        """Warm up (allocates scratch, builds run-time views) and capture one decode step in a CUDA graph."""
         check_positions(self._pos_host, 3, self.cfg.max_seq)   # two warm-up steps and the captured one
         saved_pos, saved_tok = self.pos.clone(), self.tokens.clone()
         s = torch.cuda.Stream(self.device)
@@ -396,12 +377,8 @@ class GPTQDecoder:
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         self.graph = torch.cuda.CUDAGraph()
-        if dot_path:
-            self.graph.enable_debug_mode()
         with torch.cuda.graph(self.graph):
             self._decode_step()
-        if dot_path:
-            self.graph.debug_dump(dot_path)
         self.pos.copy_(saved_pos)
         self.tokens.copy_(saved_tok)
 
@@ -416,6 +393,23 @@ class GPTQDecoder:
                 self._decode_step()
             out[i].copy_(self.tokens)
         return out
+
+    def step_kernels(self) -> dict:
+        """Run one more decode step under the framework's activity tracer and return {kernel name: launches}: what one
+        token launches on this rank (the evidence that a tensor-parallel step holds no library collective).  Not for
+        timing."""
+        import collections
+        from torch.profiler import ProfilerActivity, profile
+        torch.cuda.synchronize(self.device)
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            self.decode(1)
+            torch.cuda.synchronize(self.device)
+        counts: dict = collections.Counter()
+        for e in prof.events():
+            if e.device_type == torch.autograd.DeviceType.CUDA:
+                name = e.name.split("(")[0].replace("void ", "").replace("(anonymous namespace)::", "")
+                counts[name[:80]] += 1
+        return dict(counts)
 
     def close(self) -> None:
         """Release the peer-memory exchange (every rank, after the last step has been synchronised)."""

@@ -296,6 +296,14 @@ def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
            "allreduce": "none" if world == 1 else ("fused peer-memory exchange" if batch <= 8 else "process group")}
     if m.exchange is not None:
         out["exchange_status"] = m.exchange.status()     # 0: no wait of the fused all-reduce ever ran out
+    # what one token launches on this rank (one extra step under the activity tracer, after the timed region; every
+    # rank runs it, because the step's exchange needs all of them)
+    try:
+        kernels = m.step_kernels()
+        out["step_kernels"] = {k: v for k, v in sorted(kernels.items(), key=lambda kv: -kv[1])}
+        out["step_library_collectives"] = sum(v for k, v in kernels.items() if "nccl" in k.lower())
+    except Exception as e:   # the tracer is optional evidence, not part of the measurement
+        out["step_kernels"] = {"unavailable": repr(e)[:120]}
     m.close()
     return out
 
