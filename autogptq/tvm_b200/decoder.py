@@ -401,6 +401,9 @@ class GPTQDecoder:
         import collections
         from torch.profiler import ProfilerActivity, profile
         torch.cuda.synchronize(self.device)
+        if self._pos_host >= self.cfg.max_seq:     # the caches are full: trace a repeat of the last position
+            self._pos_host -= 1
+            self.pos.sub_(1)
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             self.decode(1)
             torch.cuda.synchronize(self.device)
