@@ -410,7 +410,7 @@ class GPTQDecoder:
         counts: dict = collections.Counter()
         for e in prof.events():
             if e.device_type == torch.autograd.DeviceType.CUDA:
-                name = e.name.split("(")[0].replace("void ", "").replace("(anonymous namespace)::", "")
+                name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
                 counts[name[:80]] += 1
         return dict(counts)
 
