@@ -141,19 +141,22 @@ class GPTQDecoder:
     """Batch of sequences, one token per step after the prompt; greedy sampling."""
 
     def __init__(self, cfg: DecoderConfig, batch: int = 1, device="cuda", group=None, fused: bool = True,
-                 single: bool = False, fused_allreduce: bool = False, fold_activation: bool = False):
+                 single: bool = False, fused_allreduce: bool = False, fold_activation: Optional[bool] = None):
         """``single=True`` builds the whole model on this device even inside a process group (the unsharded
         yardstick of a tensor-parallel run).  ``fold_activation``: decode steps of up to 8 sequences let the second
         FFN linear apply SiLU(gate) * up / ReLU as it reads its input instead of launching the element-wise kernel
-        (bit-identical; measured slower on one GPU -- 367 against 383 tok/s for Llama-7B, the activation then sits on
-        every CTA's critical path -- so it is off unless asked for)."""
+        (bit-identical).  Measured for Llama-7B: slower on one GPU (367 against 383-390 tok/s: every CTA then computes
+        the activation of its K slice between the dependency wait and its first product), faster from two GPUs on,
+        where the slices are short and a launch is a larger share of the step (536 against 508 tok/s at TP 2).
+        ``None`` picks accordingly."""
         self.cfg, self.batch = cfg, batch
-        self.fold_activation = fold_activation
+        self._fold_request = fold_activation
         self.fused = fused and cfg.head_dim in (64, 128)   # decode steps use the fused helper kernels
         self.device = torch.device(device)
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized() and not single) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.fold_activation = (self.world > 1) if self._fold_request is None else bool(self._fold_request)
         self.last_logits: Optional[torch.Tensor] = None   # this rank's slice of the latest logits [B, vocab_local]
         # fused_allreduce: the row-parallel linears and the token pick exchange through peer memory inside the
         # library's kernels instead of calling the process group (up to 8 rows; more rows still use it)
