@@ -52,6 +52,7 @@ _SIGNATURES = {
     "b200gptq_add_norm": (_c_int, [_c_void_p] * 5 + [_c_int, _c_int, ctypes.c_float, _c_int, _c_void_p]),
     "b200gptq_rope_cache": (_c_int, [_c_void_p] * 7 + [_c_int] * 5 + [_c_void_p]),
     "b200gptq_attn_decode": (_c_int, [_c_void_p] * 5 + [_c_int] * 4 + [ctypes.c_float, _c_void_p]),
+    "b200gptq_attn_step": (_c_int, [_c_void_p] * 7 + [_c_int] * 5 + [ctypes.c_float, _c_void_p]),
     "b200gptq_act": (_c_int, [_c_void_p] * 2 + [_c_int] * 3 + [_c_void_p]),
     "b200gptq_dense_gemv": (_c_int, [_c_void_p] * 3 + [_c_int] * 3 + [_c_void_p]),
 }

@@ -177,23 +177,62 @@ __device__ __forceinline__ void cluster_sync_all() {
 // 32 positions; values: each lane owns HD/32 dims, the 32 probabilities are broadcast by shuffle and the
 // 32 value rows are read coalesced.  Online softmax per warp; warps are combined through shared memory
 // and the CTAs of the cluster through distributed shared memory by the cluster's first CTA.
+//
+// STEP = true is the whole attention part of a decode step in one launch: `q` is then qkv[b, 3, heads, hd] of the
+// new token; every CTA rotates q and the new k itself (the same fp16 arithmetic as rope_cache_kernel), uses the new
+// k and v from shared memory for position pos[0], and the cluster's first CTA writes them into the caches for the
+// steps to come -- rope_cache_kernel + attn_decode_kernel without the launch in between.
 constexpr int kAttnSplit = 4;
-template <int HD>
+template <int HD, bool STEP>
 __global__ void __launch_bounds__(512)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
-                   const __half* __restrict__ v_cache, const long long* __restrict__ pos,
-                   __half* __restrict__ out, int heads, int max_seq, float scale) {
+                   const __half* __restrict__ v_cache, const long long* __restrict__ pos, __half* __restrict__ out,
+                   int heads, int max_seq, float scale, const __half* __restrict__ cos_t,
+                   const __half* __restrict__ sin_t, int rope, __half* k_write, __half* v_write) {
+    // k_write / v_write (STEP): the same caches, for the one row this kernel writes; that row is never read through
+    // k_cache / v_cache here (position pos[0] is served from shared memory), so the read-only path stays valid.
     constexpr int PER = HD / 32, WARPS = 16;
     __shared__ __align__(16) __half q_sm[HD];
+    __shared__ __align__(16) __half knew_sm[STEP ? HD : 8], vnew_sm[STEP ? HD : 8];
     __shared__ float sm_m[WARPS], sm_l[WARPS], sm_acc[WARPS][HD];
     __shared__ float cta_m, cta_l, cta_acc[HD];   // this CTA's partial result, read by the cluster's first CTA
     pdl_enter();
     const int split = blockIdx.x % kAttnSplit, head = blockIdx.x / kAttnSplit, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long p64 = pos[0];
-    const int L = p64 < 0 ? 0 : (p64 >= max_seq ? max_seq : (int)p64 + 1);   // never past the end of the caches
+    if (STEP && (p64 < 0 || p64 >= max_seq)) return;   // a position outside the caches: refused by the whole cluster
+    const int P = STEP ? (int)p64 : -1;                // the position whose key and value are in shared memory
+    // positions served from the caches: 0..pos[0] (never past their end); STEP: 0..pos[0]-1, the new one comes last
+    const int L = STEP ? P : (p64 < 0 ? 0 : (p64 >= max_seq ? max_seq : (int)p64 + 1));
     const size_t base = ((size_t)b * heads + head) * (size_t)max_seq * HD;
-    if (threadIdx.x < HD) q_sm[threadIdx.x] = q[((size_t)b * heads + head) * HD + threadIdx.x];
+    if constexpr (STEP) {
+        if (threadIdx.x < HD / 2) {
+            const int i = threadIdx.x;   // pair index
+            const size_t tok = (size_t)b * 3 * heads * HD;
+            const __half2 q2 = *reinterpret_cast<const __half2*>(q + tok + (size_t)head * HD + 2 * i);
+            const __half2 k2 = *reinterpret_cast<const __half2*>(q + tok + (size_t)(heads + head) * HD + 2 * i);
+            const __half2 v2 = *reinterpret_cast<const __half2*>(q + tok + (size_t)(2 * heads + head) * HD + 2 * i);
+            float2 qf = __half22float2(q2), kf = __half22float2(k2);
+            if (rope) {
+                const __half c = cos_t[(size_t)P * (HD / 2) + i], sn = sin_t[(size_t)P * (HD / 2) + i];
+                const __half q0 = __hsub(__hmul(q2.x, c), __hmul(q2.y, sn)), q1 = __hadd(__hmul(q2.x, sn), __hmul(q2.y, c));
+                const __half k0 = __hsub(__hmul(k2.x, c), __hmul(k2.y, sn)), k1 = __hadd(__hmul(k2.x, sn), __hmul(k2.y, c));
+                qf = make_float2(__half2float(q0), __half2float(q1));
+                kf = make_float2(__half2float(k0), __half2float(k1));
+            }
+            const __half2 kr = __floats2half2_rn(kf.x, kf.y);
+            *reinterpret_cast<__half2*>(q_sm + 2 * i) = __floats2half2_rn(qf.x, qf.y);
+            *reinterpret_cast<__half2*>(knew_sm + 2 * i) = kr;
+            *reinterpret_cast<__half2*>(vnew_sm + 2 * i) = v2;
+            if (split == 0) {
+                const size_t c_off = base + (size_t)P * HD + 2 * i;
+                *reinterpret_cast<__half2*>(k_write + c_off) = kr;
+                *reinterpret_cast<__half2*>(v_write + c_off) = v2;
+            }
+        }
+    } else {
+        if (threadIdx.x < HD) q_sm[threadIdx.x] = q[((size_t)b * heads + head) * HD + threadIdx.x];
+    }
     __syncthreads();
     float acc[PER];
 #pragma unroll
@@ -246,6 +285,20 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
                 acc[0] = fmaf(p, a.x, acc[0]); acc[1] = fmaf(p, a.y, acc[1]);
             }
         }
+    }
+    if (STEP && split == 0 && warp == 0) {
+        // the new position: key and value are in shared memory; one more step of the online softmax for this warp
+        float part = 0.f;
+#pragma unroll
+        for (int d = 0; d < PER; ++d)
+            part = fmaf(__half2float(knew_sm[lane * PER + d]), __half2float(q_sm[lane * PER + d]), part);
+        const float dot = warp_sum(part) * scale;
+        const float m_new = fmaxf(m, dot);
+        const float pexp = __expf(dot - m_new), corr = __expf(m - m_new);
+        l = l * corr + pexp;
+        m = m_new;
+#pragma unroll
+        for (int d = 0; d < PER; ++d) acc[d] = fmaf(pexp, __half2float(vnew_sm[lane * PER + d]), acc[d] * corr);
     }
     if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
 #pragma unroll
@@ -418,12 +471,40 @@ B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const 
     const long long* ph = static_cast<const long long*>(pos);
     __half* oh = static_cast<__half*>(out);
     const dim3 grid(heads * kAttnSplit, batch);
+    const __half* none = nullptr;
+    __half* nowrite = nullptr;
     if (hd == 128) {
-        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<128>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph, oh,
-                                     heads, max_seq, scale));
+        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<128, false>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
+                                     oh, heads, max_seq, scale, none, none, 0, nowrite, nowrite));
     } else {
-        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<64>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph, oh,
-                                     heads, max_seq, scale));
+        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<64, false>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
+                                     oh, heads, max_seq, scale, none, none, 0, nowrite, nowrite));
+    }
+    B200GPTQ_CUDA_TRY(cudaGetLastError());
+    return B200GPTQ_OK;
+}
+
+B200GPTQ_API int b200gptq_attn_step(const void* qkv, const void* cos_t, const void* sin_t, const void* pos,
+                                    void* k_cache, void* v_cache, void* out, int batch, int heads, int hd,
+                                    int max_seq, int rope, float scale, void* stream) {
+    if (!qkv || !k_cache || !v_cache || !pos || !out || (rope && (!cos_t || !sin_t))) return B200GPTQ_ERR_NULL_POINTER;
+    if (batch <= 0 || heads <= 0 || (hd != 64 && hd != 128)) return B200GPTQ_ERR_SHAPE;
+    const __half* qh = static_cast<const __half*>(qkv);
+    const __half* kh = static_cast<const __half*>(k_cache);
+    const __half* vh = static_cast<const __half*>(v_cache);
+    const __half* ch = static_cast<const __half*>(cos_t);
+    const __half* sh = static_cast<const __half*>(sin_t);
+    const long long* ph = static_cast<const long long*>(pos);
+    __half* oh = static_cast<__half*>(out);
+    const dim3 grid(heads * kAttnSplit, batch);
+    if (hd == 128) {
+        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<128, true>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
+                                     oh, heads, max_seq, scale, ch, sh, rope, static_cast<__half*>(k_cache),
+                                     static_cast<__half*>(v_cache)));
+    } else {
+        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<64, true>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
+                                     oh, heads, max_seq, scale, ch, sh, rope, static_cast<__half*>(k_cache),
+                                     static_cast<__half*>(v_cache)));
     }
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;

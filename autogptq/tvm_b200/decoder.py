@@ -348,10 +348,9 @@ class GPTQDecoder:
         for L in self.layers:
             ops.add_norm(x, delta, L.norm1_w, L.norm1_b, h, eps, rms)
             qkv = L.qkv(h)
-            q = torch.empty((B, L.heads_local * hd), dtype=torch.float16, device=self.device)
-            ops.rope_cache(qkv, self.cos, self.sin, self.pos, q, L.k_cache, L.v_cache, L.heads_local, hd, rms)
-            att = torch.empty_like(q)
-            ops.attn_decode(q, L.k_cache, L.v_cache, self.pos, att, L.heads_local, hd)
+            att = torch.empty((B, L.heads_local * hd), dtype=torch.float16, device=self.device)
+            # rotary embedding, cache write and single-query attention in one launch
+            ops.attn_step(qkv, self.cos, self.sin, self.pos, L.k_cache, L.v_cache, att, L.heads_local, hd, rms)
             o = self._row(L.o, att)
             ops.add_norm(x, o, L.norm2_w, L.norm2_b, h, eps, rms)
             u = L.up(h)

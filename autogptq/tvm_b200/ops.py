@@ -338,6 +338,18 @@ def attn_decode(q, k_cache, v_cache, pos, out, heads: int, hd: int):
     return out
 
 
+def attn_step(qkv, cos_t, sin_t, pos, k_cache, v_cache, out, heads: int, hd: int, rope: bool):
+    """:func:`rope_cache` and :func:`attn_decode` as one launch (``b200gptq_attn_step``): ``qkv`` ``[B, 3*heads*hd]`` of
+    the new token in, attention output ``[B, heads*hd]`` out, caches updated at position ``pos[0]``."""
+    B, max_seq = k_cache.shape[0], k_cache.shape[2]
+    with torch.cuda.device(qkv.device):
+        st = _lib.lib.b200gptq_attn_step(_ptr(qkv), _ptr(cos_t), _ptr(sin_t), _ptr(pos), _ptr(k_cache), _ptr(v_cache),
+                                         _ptr(out), B, heads, hd, max_seq, 1 if rope else 0, 1.0 / (hd ** 0.5),
+                                         _stream(qkv.device))
+    _lib.check(st, "b200gptq_attn_step")
+    return out
+
+
 def act(u, out, inter: int, gated: bool):
     with torch.cuda.device(u.device):
         st = _lib.lib.b200gptq_act(_ptr(u), _ptr(out), u.shape[0], inter, 1 if gated else 0, _stream(u.device))

@@ -328,6 +328,10 @@ B200GPTQ_API int b200gptq_tp_probe(const void* device_ptr, unsigned int* host_ou
  *   b200gptq_rope_cache   one new token per sequence: qkv[b,3,heads,hd] -> rotated q_out[b,heads,hd]; rotated k
  *                         and v written at position pos[0] of the caches [b,heads,max_seq,hd]; rope == 0: no rotation
  *   b200gptq_attn_decode  out[b,heads*hd] = softmax(q k^T * scale) v over cache positions 0..pos[0]; hd in {64,128}
+ *   b200gptq_attn_step    b200gptq_rope_cache followed by b200gptq_attn_decode as ONE launch (same caches bit for bit,
+ *                         same output up to the order of the softmax accumulation): rotates
+ *                         q and the new k inside the attention kernel, attends to the new position from shared
+ *                         memory and writes k, v into the caches for the steps to come
  *   b200gptq_act          act[rows,I] = silu(u[:, :I]) * u[:, I:] (gated != 0) or relu(u) (gated == 0)
  * `pos` is a device pointer to one int64, so that a captured graph can advance it.
  */
@@ -339,6 +343,9 @@ B200GPTQ_API int b200gptq_rope_cache(const void* qkv, const void* cos_t, const v
 B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos,
                                       void* out, int batch, int heads, int hd, int max_seq, float scale,
                                       void* stream);
+B200GPTQ_API int b200gptq_attn_step(const void* qkv, const void* cos_t, const void* sin_t, const void* pos,
+                                    void* k_cache, void* v_cache, void* out, int batch, int heads, int hd,
+                                    int max_seq, int rope, float scale, void* stream);
 B200GPTQ_API int b200gptq_act(const void* u, void* act, int rows, int I, int gated, void* stream);
 
 /*

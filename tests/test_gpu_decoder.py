@@ -124,3 +124,31 @@ def test_folded_activation_gives_the_same_tokens(arch, bits, desc_act, batch):
     m = decoder.GPTQDecoder(cfg, batch=batch, device=DEV, fold_activation=True)
     folds = [L.down.can_fold(batch, 1 if arch == "llama" else 2) for L in m.layers]
     assert all(folds), "the miniature's FFN layers are expected to take the folded activation"
+
+
+@pytest.mark.parametrize("hd,rope,B,heads,pos", [(128, True, 1, 4, 37), (64, False, 3, 6, 0), (128, True, 2, 3, 255), (64, True, 1, 2, 100)])
+def test_attention_step_equals_its_two_kernels(hd, rope, B, heads, pos):
+    """b200gptq_attn_step (rotary + cache write + attention in one launch) against b200gptq_rope_cache followed by
+    b200gptq_attn_decode: the same caches bit for bit, the same attention output up to the order in which the new
+    position enters the online softmax."""
+    max_seq = 256
+    g = torch.Generator().manual_seed(hd + pos)
+    qkv = torch.randn(B, 3 * heads * hd, generator=g).half().to(DEV)
+    kc = torch.randn(B, heads, max_seq, hd, generator=g).half().to(DEV)
+    vc = torch.randn(B, heads, max_seq, hd, generator=g).half().to(DEV)
+    ang = torch.arange(max_seq).float()[:, None] * (1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd)))[None, :]
+    cos, sin = ang.cos().half().to(DEV), ang.sin().half().to(DEV)
+    p = torch.tensor([pos], dtype=torch.long, device=DEV)
+    k1, v1 = kc.clone(), vc.clone()
+    q = torch.empty(B, heads * hd, dtype=torch.float16, device=DEV)
+    ops.rope_cache(qkv, cos, sin, p, q, k1, v1, heads, hd, rope)
+    want = ops.attn_decode(q, k1, v1, p, torch.empty_like(q), heads, hd)
+    k2, v2 = kc.clone(), vc.clone()
+    got = ops.attn_step(qkv, cos, sin, p, k2, v2, torch.empty_like(q), heads, hd, rope)
+    assert torch.allclose(got.float(), want.float(), rtol=2e-3, atol=2e-3)
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)
+    # a position outside the caches is refused without touching them
+    bad = torch.tensor([max_seq], dtype=torch.long, device=DEV)
+    k3 = kc.clone()
+    ops.attn_step(qkv, cos, sin, bad, k3, vc.clone(), torch.empty_like(q), heads, hd, rope)
+    assert torch.equal(k3, kc)
