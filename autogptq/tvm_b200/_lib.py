@@ -49,6 +49,7 @@ _SIGNATURES = {
     "b200gptq_tp_probe": (_c_int, [_c_void_p, _c_void_p]),
     "b200gptq_gemv_static": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p]),
     "b200gptq_gemv_static_capacity": (_c_size_t, []),
+    "b200gptq_gemv_static_status": (_c_int, [_c_void_p, _c_void_p]),
     "b200gptq_add_norm": (_c_int, [_c_void_p] * 5 + [_c_int, _c_int, ctypes.c_float, _c_int, _c_void_p]),
     "b200gptq_rope_cache": (_c_int, [_c_void_p] * 7 + [_c_int] * 5 + [_c_void_p]),
     "b200gptq_attn_decode": (_c_int, [_c_void_p] * 5 + [_c_int] * 4 + [ctypes.c_float, _c_void_p]),

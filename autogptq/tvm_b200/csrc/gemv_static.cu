@@ -93,4 +93,12 @@ int b200gptq_gemv_static(const void* x, const int32_t* qweight, const int32_t* q
                                  group_size, scratch, s);
 }
 
+// The sticky status word of the built-in scratch on the current device (see b200gptq_workspace_status).
+int b200gptq_gemv_static_status(void* stream, unsigned int* host_out) {
+    if (!host_out) return B200GPTQ_ERR_NULL_POINTER;
+    void* scratch = nullptr;
+    if (int st = static_scratch(&scratch)) return st;
+    return b200gptq_workspace_status(scratch, stream, host_out);
+}
+
 }  // extern "C"

@@ -86,7 +86,7 @@ B200GPTQ_API size_t b200gptq_workspace_bytes(int op, int M, int K, int N, int bi
  * cycles); a kernel whose wait runs out raises this word to a non-zero value, finishes with undefined results
  * and returns, so the context stays usable.  The call copies the word to `*host_out` and SYNCHRONISES the
  * stream.  0 = no wait ever ran out since the buffer was zero-filled.  (The word is the last 32-bit word of
- * the first 16 KiB of the buffer; b200gptq_gemv_static keeps its scratch private and has no such query.)
+ * the first 16 KiB of the buffer; b200gptq_gemv_static_status is the same query for the scratch built into the library.)
  */
 B200GPTQ_API int b200gptq_workspace_status(const void* workspace, void* stream, unsigned int* host_out);
 
@@ -252,6 +252,8 @@ B200GPTQ_API int b200gptq_gemv_static(const void* x, const int32_t* qweight, con
 
 /* Bytes of the built-in scratch array used by b200gptq_gemv_static (per device). */
 B200GPTQ_API size_t b200gptq_gemv_static_capacity(void);
+/* b200gptq_workspace_status for the built-in scratch of the current device (synchronises the stream). */
+B200GPTQ_API int b200gptq_gemv_static_status(void* stream, unsigned int* host_out);
 
 /*
  * Tensor-parallel row shards (one process per GPU of one node): the decode GEMV of a K shard with the sum

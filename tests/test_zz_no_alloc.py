@@ -72,3 +72,12 @@ def test_capacity_is_enforced():
     # the same problem still runs with caller-provided scratch
     y = ops.gemv(x, layer.qweight, layer.qzeros, layer.scales, None, bits, 128)
     assert bool(torch.isfinite(y.float()).all())
+
+
+def test_status_of_the_built_in_scratch_is_clear():
+    """b200gptq_gemv_static_status: no bounded wait of a kernel that used the built-in scratch has run out."""
+    import ctypes
+    word = ctypes.c_uint(7)
+    with torch.cuda.device(0):
+        st = _lib.lib.b200gptq_gemv_static_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(word))
+    assert st == 0 and word.value == 0
