@@ -40,15 +40,17 @@ constexpr int BN = 128;                 // output columns per CTA = rows of the 
 constexpr int BK = 64;                  // rows of K per stage
 constexpr int kMaxTN = 256;             // rows of x per CTA = N of the MMA
 constexpr int kWeightWarps = 8;         // warps that build one k-tile's A operand
-constexpr int kWeightGroups = 3;        // groups of such warps, taking k-tiles in turn
-constexpr int kMmaWarp = 1 + kWeightWarps * kWeightGroups;
-constexpr int kGemmThreads = 32 * (2 + kWeightWarps * kWeightGroups);  // TMA warp, weight warps, MMA warp
+// Groups of weight warps, taking k-tiles in turn.
+__host__ __device__ constexpr int mma_warp(int groups) { return 1 + kWeightWarps * groups; }
+__host__ __device__ constexpr int gemm_threads(int groups) { return 32 * (2 + kWeightWarps * groups); }  // TMA warp, weight warps, MMA warp
 constexpr int kPackedTileBytes = 4096;  // up to 8 word-rows x 128 columns of packed weights per k-tile
 constexpr int kMaxStages = 16;
 constexpr int kTmemCols = 512;          // accumulators in columns [0, TN), A buffers behind them (as many stages as fit)
 constexpr int kTmemAColsPerStage = 32;  // 64 k x fp16 = 32 columns of 32 bits
 constexpr int kSmemBudget = 222 * 1024;  // ring bytes; the opt-in maximum per CTA is 227 KB
 constexpr int kStatusWord = kMaxCounters - 1;  // sticky error word inside the counter region
+constexpr int kMaxSplits = 4;            // CTAs that share the k-tiles of one output tile (split K)
+constexpr int kGroups = 3;               // weight groups of the launched kernel
 
 // 3-bit: order in which the 32 fields of a row block leave the 7-window unpack (pairs are
 // adjacent entries).  x is permuted the same way by the pre-pass.
@@ -227,12 +229,16 @@ prep_x_kernel(const __half* __restrict__ x, const int32_t* __restrict__ x_perm, 
     }
 }
 
-template <int BITS>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BITS, int kWeightGroups>
+__global__ void __launch_bounds__(gemm_threads(kWeightGroups), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
             const int32_t* __restrict__ g_idx, const __half* __restrict__ bias, __half* __restrict__ y, int M, int K,
-            int N, int group_size, int TN, int S, int tab_groups, int a_off, unsigned int* __restrict__ status) {
+            int N, int group_size, int TN, int S, int tab_groups, int a_off, unsigned int* __restrict__ status,
+            int splits, int tmem_cols, float* __restrict__ partial) {
+    // splits > 1 (few rows of x, fewer column tiles than SMs): blockIdx.z takes a contiguous run of the k-tiles, two
+    // such CTAs fit on an SM (half of the shared and tensor memory each), every CTA leaves its fp32 sums in
+    // `partial[z][row][column]`, and the last one of a tile to arrive adds them up in the order of z.
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;            // swizzled tiles need 1024-byte alignment
@@ -240,10 +246,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     __shared__ __align__(8) uint64_t bars[3 * kMaxStages + 1];  // tma[S], a_full[S], empty[S], accum
     __shared__ uint32_t tmem_base_holder;
     __shared__ volatile int abort_flag;
+    __shared__ volatile int epi_bad;      // split K: an epilogue warp's wait ran out
+    __shared__ unsigned int arrived;     // split K: CTAs of this tile that had arrived before this one
 
+    constexpr int kMmaWarp = mma_warp(kWeightGroups);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.y * BN, m0 = blockIdx.x * TN;
-    const int KT = (K + BK - 1) / BK;
+    const int KT_all = (K + BK - 1) / BK;
+    const int kt_first = (int)(((long long)blockIdx.z * KT_all) / splits);
+    const int KT = (int)(((long long)(blockIdx.z + 1) * KT_all) / splits) - kt_first;   // k-tiles of this CTA
     const uint32_t x_tile_bytes = (uint32_t)TN * BK * 2;
     const uint32_t stage_bytes = x_tile_bytes + kPackedTileBytes;
 
@@ -259,6 +270,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        epi_bad = 0;
         for (int s = 0; s < S; ++s) {
             mbar_init(tma_bar(s), 1);               // the TMA producer's expect_tx arrive
             mbar_init(full_bar(s), kWeightWarps);   // one arrive per weight warp
@@ -269,7 +281,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_holder)), "r"((uint32_t)kTmemCols) : "memory");
+                     ::"r"(smem_u32(&tmem_base_holder)), "r"((uint32_t)tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -284,8 +296,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             for (int kt = 0; kt < KT; ++kt) {
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, &abort_flag)) break;
                 mbar_arrive_expect_tx(tma_bar(s), x_tile_bytes + kPackedBytes);
-                tma_load_2d(p_tile(s), &tmap_w, n0, kt * kWordRowsPerTile, tma_bar(s));
-                tma_load_2d(x_tile(s), &tmap_x, kt * BK, m0, tma_bar(s));
+                tma_load_2d(p_tile(s), &tmap_w, n0, (kt_first + kt) * kWordRowsPerTile, tma_bar(s));
+                tma_load_2d(x_tile(s), &tmap_x, (kt_first + kt) * BK, m0, tma_bar(s));
                 if (++s == S) { s = 0; ++round; }
             }
         }
@@ -361,12 +373,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         };
         int g_cur = -1, g_nxt = -1, z_cur = 0, z_nxt = 0;
         __half s_cur = __float2half(0.f), s_nxt = __float2half(0.f);
-        load_group(2 * wgroup + kh, g_cur, s_cur, z_cur);
+        load_group(2 * (kt_first + wgroup) + kh, g_cur, s_cur, z_cur);
 
         bool ok = true;
         int s = wgroup % S, round = wgroup / S;
         for (int kt = wgroup; kt < KT; kt += kWeightGroups) {
-            const int rb = 2 * kt + kh;
+            const int rb = 2 * (kt_first + kt) + kh;
             // fetch the scale / zero-point of this thread's next k-tile now, a whole iteration ahead of their use
             constexpr int kRbStep = 2 * kWeightGroups;
             if (rb + kRbStep < RB && col_ok) {
@@ -407,21 +419,79 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         // ----- epilogue: accumulators (lane = output column, column = row of x) -> fp16 -> y -----
         if (ok) ok = mbar_wait(accum_bar, 0, &abort_flag);
         ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float b = (bias && col_ok) ? __half2float(bias[n]) : 0.f;
+        const float b = (bias && col_ok) ? __half2float(bias[n]) : 0.f;
+        constexpr int kEpiWarps = kWeightWarps * kWeightGroups;
+        if (splits == 1) {
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            // the warps that share a lane quarter take the 16-row chunks in turn
-            for (int c = (warp - 1) >> 2; c < TN / 16; c += kWeightWarps * kWeightGroups / 4) {
-                uint32_t r[16];
-                tmem_ld16(lane_addr + 16u * c, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int m = m0 + 16 * c;
-                if (col_ok) {
+                // the warps that share a lane quarter take the 16-row chunks in turn
+                for (int c = (warp - 1) >> 2; c < TN / 16; c += kEpiWarps / 4) {
+                    uint32_t r[16];
+                    tmem_ld16(lane_addr + 16u * c, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int m = m0 + 16 * c;
+                    if (col_ok) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (m + i < M) y[(size_t)(m + i) * N + n] = __float2half_rn(__uint_as_float(r[i]) + b);
+                        for (int i = 0; i < 16; ++i)
+                            if (m + i < M) y[(size_t)(m + i) * N + n] = __float2half_rn(__uint_as_float(r[i]) + b);
+                    }
                 }
+            }
+        } else {
+            // ---- split K: fp32 sums of this CTA's k-tiles to the scratch, then the last CTA of the tile adds them.
+            //      The hardware barriers below are reached by all epilogue warps whatever happened before: a CTA whose
+            //      wait ran out still counts itself in, so that the tile's counter returns to zero (the results are then
+            //      undefined and the status word says so). ----
+            if (!ok && lane == 0) epi_bad = 1;
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+            const int rows_pad = gridDim.x * TN;
+            if (epi_bad == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float* mine = partial + (size_t)blockIdx.z * rows_pad * N;
+#pragma unroll 1
+                for (int c = (warp - 1) >> 2; c < TN / 16; c += kEpiWarps / 4) {
+                    uint32_t r[16];
+                    tmem_ld16(lane_addr + 16u * c, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int m = m0 + 16 * c;
+                    if (col_ok) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (m + i < M) mine[(size_t)(m + i) * N + n] = __uint_as_float(r[i]);
+                    }
+                }
+            }
+            __threadfence();   // this thread's sums are visible before the tile's arrival is counted
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+            unsigned int* counter = status + (blockIdx.y * gridDim.x + blockIdx.x);
+            if (threadIdx.x == 32) arrived = atomicAdd(counter, 1u);
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+            if (arrived == (unsigned int)splits - 1u) {
+                __threadfence();   // the other CTAs' sums, published before their arrivals
+#pragma unroll 1
+                for (int c = (warp - 1) >> 2; c < TN / 16; c += kEpiWarps / 4) {
+                    const int m = m0 + 16 * c;
+                    if (col_ok) {
+                        // all loads of the chunk are issued before the first is used: one round trip to L2, not 64
+                        float v[kMaxSplits][16];
+#pragma unroll
+                        for (int z = 0; z < kMaxSplits; ++z)
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                v[z][i] = (z < splits && m + i < M)
+                                              ? __ldcg(partial + ((size_t)z * rows_pad + m + i) * N + n) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (m + i < M) {
+                                float sum = v[0][i];
+#pragma unroll
+                                for (int z = 1; z < kMaxSplits; ++z) sum += v[z][i];   // in the order of z
+                                y[(size_t)(m + i) * N + n] = __float2half_rn(sum + b);
+                            }
+                    }
+                }
+                if (threadIdx.x == 32) *counter = 0u;   // the counter region is left as it was found
             }
         }
     }
@@ -431,7 +501,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     __syncthreads();
     if (threadIdx.x == 0 && abort_flag) atomicExch(status + kStatusWord, 1u);
     if (warp == kMmaWarp) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
     }
 }
 
@@ -452,6 +522,33 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Split K: with few rows of x a tile's time is the chain of hand-overs per k-tile, not its arithmetic, and a layer
+// with fewer than #SM / 2 column tiles leaves SMs idle; the k-tiles of a tile are then spread over as many CTAs as
+// there are idle SMs per tile (up to kMaxSplits).  Only for one row tile (M <= 128) and when every split keeps at
+// least 16 k-tiles (40 above 64 rows).  (Two split CTAs per SM were measured too, with two weight groups and half of the shared and
+// tensor memory each: 37.7 us against 33.5 us for 16 rows of the 4096 x 12288 layer -- what bounds a k-tile is shared
+// by the CTAs of an SM -- so a split never puts two CTAs on one SM.)
+int pick_splits(int M, int N, int K) {
+    if (M > 128) return 1;
+    const int tiles = (N + BN - 1) / BN;
+    if (tiles >= kMaxCounters - 1) return 1;
+    int sp = sm_count() / tiles;
+    if (sp > kMaxSplits) sp = kMaxSplits;
+    const int KT = (K + BK - 1) / BK;
+    // every split keeps enough k-tiles to pay for its own start-up and for the final sum (more with taller tiles,
+    // whose partial sums are larger): measured on 4096 x 4096, 16 rows 33.5 -> 26 us with four splits, 128 rows
+    // 34.6 -> 37.4 us with two
+    const int min_tiles = M <= 64 ? 16 : 40;
+    while (sp > 1 && KT / sp < min_tiles) --sp;
+    return sp < 1 ? 1 : sp;
+}
+size_t split_partial_bytes(int M, int N, int K) {
+    const int sp = pick_splits(M, N, K);
+    if (sp == 1) return 0;
+    const int TN = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+    return (size_t)sp * TN * N * sizeof(float);
+}
+
 int pick_tn(int M) {
     if (M <= 16) return 16;
     if (M <= 32) return 32;
@@ -463,7 +560,7 @@ int pick_tn(int M) {
 template <int BITS>
 int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                 const int32_t* g_idx, const __half* bias, __half* y, int M, int K, int N, int group_size,
-                unsigned int* status, cudaStream_t stream) {
+                unsigned int* status, float* partial, cudaStream_t stream) {
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) { set_last_cuda_error((int)cudaErrorNotSupported); return B200GPTQ_ERR_CUDA; }
     const int TN = pick_tn(M);
@@ -471,16 +568,20 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
     // scale / zero-point table of the CTA's columns for every group, if it leaves room for >= 4 stages
     const int gs_eff = group_size;
     const int G = (K + gs_eff - 1) / gs_eff;
+    const int splits = pick_splits(M, N, K);
+    const int smem_budget = kSmemBudget;
+    const int tmem_cols = kTmemCols;
     int tab_bytes = G * BN * 4 + ((K / 32 * 2 + 15) / 16) * 16;
     int tab_groups = G;
-    if (G > 65535 || kSmemBudget - tab_bytes < 4 * stage_bytes) { tab_bytes = 0; tab_groups = 0; }
+    if (G > 65535 || smem_budget - tab_bytes < 4 * stage_bytes) { tab_bytes = 0; tab_groups = 0; }
     // Stages: a small-M tile moves 4..6 KB per k-tile and its round trip (TMA, dequantisation, MMA, commit) lasts
     // microseconds, so throughput is the number of k-tiles in flight: as many as shared memory and the tensor-memory
     // columns behind the accumulators hold.
     const int a_off = TN < 32 ? 32 : TN;
-    int S = (kSmemBudget - tab_bytes) / stage_bytes;
+    int S = (smem_budget - tab_bytes) / stage_bytes;
     if (S > kMaxStages) S = kMaxStages;
-    if (S > (kTmemCols - a_off) / kTmemAColsPerStage) S = (kTmemCols - a_off) / kTmemAColsPerStage;
+    if (S > (tmem_cols - a_off) / kTmemAColsPerStage) S = (tmem_cols - a_off) / kTmemAColsPerStage;
+    if (S < 2) return B200GPTQ_ERR_TOO_LARGE;
     const int smem_bytes = S * stage_bytes + tab_bytes + 1024;  // + slack to align the ring to 1024 bytes
 
     CUtensorMap tmap_x, tmap_w;
@@ -510,14 +611,15 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
     int dev = 0;
     B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B200GPTQ_ERR_TOO_LARGE;
-    auto kernel = gemm_kernel<BITS>;
-    std::call_once(attr_once[dev], [dev, kernel] {
-        attr_result[dev] = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    std::call_once(attr_once[dev], [dev] {
+        attr_result[dev] = (int)cudaFuncSetAttribute(gemm_kernel<BITS, kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     226 * 1024);
     });
     if (attr_result[dev] != 0) { set_last_cuda_error(attr_result[dev]); return B200GPTQ_ERR_CUDA; }
-    dim3 grid((M + TN - 1) / TN, (N + BN - 1) / BN);
-    kernel<<<grid, kGemmThreads, smem_bytes, stream>>>(tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N,
-                                                     group_size, TN, S, tab_groups, a_off, status);
+    dim3 grid((M + TN - 1) / TN, (N + BN - 1) / BN, splits);
+    gemm_kernel<BITS, kGroups><<<grid, gemm_threads(kGroups), smem_bytes, stream>>>(
+        tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N, group_size, TN, S, tab_groups, a_off, status, splits,
+        tmem_cols, partial);
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
 }
@@ -527,8 +629,9 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
 // Scratch: the counter region (its last word is the sticky status word) and, when x has to be
 // gathered or permuted, a copy of x.
 size_t gemm_workspace_bytes(int M, int K, int N, int bits) {
-    (void)N; (void)bits;
-    return kCounterBytes + (size_t)M * K * sizeof(__half);
+    (void)bits;
+    // counters | copy of x (gathered / permuted) | fp32 partial sums of a split-K launch
+    return kCounterBytes + (((size_t)M * K * sizeof(__half) + 255) & ~(size_t)255) + split_partial_bytes(M, N, K);
 }
 
 int gemm_dispatch(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
@@ -547,8 +650,10 @@ int gemm_dispatch(const __half* x, const int32_t* qweight, const int32_t* qzeros
         B200GPTQ_CUDA_TRY(cudaGetLastError());
         xt = xp;
     }
-    if (bits == 4) return launch_gemm<4>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream);
-    if (bits == 3) return launch_gemm<3>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, stream);
+    float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes +
+                                              (((size_t)M * K * sizeof(__half) + 255) & ~(size_t)255));
+    if (bits == 4) return launch_gemm<4>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, partial, stream);
+    if (bits == 3) return launch_gemm<3>(xt, qweight, qzeros, scales, g_idx, bias, y, M, K, N, group_size, status, partial, stream);
     return B200GPTQ_ERR_BITS;
 }
 

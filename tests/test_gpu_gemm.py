@@ -58,6 +58,33 @@ def test_gemm_vs_oracle(bits, K, N, gs, M, bias):
     _status_clear()
 
 
+SPLIT_K_CASES = [
+    # bits, K, N, gs, M, bias: few column tiles and a long K, so that several CTAs share one output tile
+    (4, 4096, 1024, 128, 16, True),      # 8 column tiles, four runs of 16 k-tiles
+    (3, 4096, 512, 128, 48, False),
+    (4, 8192, 256, 128, 100, True),      # above 64 rows: three runs of unequal length (128 k-tiles)
+    (4, 2112, 128, 32, 20, False),       # 33 k-tiles: runs of 16 and 17
+    (3, 6144, 384, -1, 7, True),
+]
+
+
+@pytest.mark.parametrize("bits,K,N,gs,M,bias", SPLIT_K_CASES)
+def test_gemm_with_k_split_over_ctas_vs_oracle(bits, K, N, gs, M, bias):
+    """Up to 128 rows and fewer column tiles than SMs: K is cut into runs, one CTA per run, and the last CTA of a
+    tile to finish sums the fp32 partial sums in run order.  Same oracle and tolerance as the unsplit kernel; the
+    result must not depend on which CTA arrives last, and the tile counters must be back at zero for the next call."""
+    layer = synth.make_layer(bits, K, N, gs, False, bias=bias, seed=K + N + M)
+    x = synth.make_x(M, K, seed=M)
+    _, _, W = O.dequantize(*_layer_np(layer), bits)
+    d = layer.to(DEV)
+    xd = x.to(DEV)
+    y = ops.gemm(xd, d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias)
+    _check(y, x.numpy(), W, None if layer.bias is None else layer.bias.numpy())
+    for _ in range(5):
+        assert torch.equal(y, ops.gemm(xd, d.qweight, d.qzeros, d.scales, None, bits, gs, bias=d.bias))
+    _status_clear()
+
+
 @pytest.mark.parametrize("bits,K,N,gs,M", [(4, 1024, 256, 128, 40), (3, 1024, 256, 128, 150), (4, 512, 160, 64, 17)])
 def test_gemm_act_order_through_quantlinear(bits, K, N, gs, M):
     layer = synth.make_layer(bits, K, N, gs, act_order=True, seed=3 * bits + M)
