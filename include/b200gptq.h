@@ -193,6 +193,10 @@ B200GPTQ_API int b200gptq_gemv_path(int M, int K, int N, int bits, int group_siz
  *
  * x_perm as for b200gptq_gemv, except that a non-NULL x_perm needs
  * workspace room for the gathered copy of x (counted by b200gptq_workspace_bytes).
+ * With M <= 128 and fewer column tiles than SMs, K is split over up to four
+ * thread blocks per tile; their fp32 partial sums live in the workspace (also
+ * counted by b200gptq_workspace_bytes) and are added in a fixed order, so the
+ * result does not depend on which block finishes last.
  * g_idx must be constant over aligned 32-row blocks: the kernel takes the
  * group of a block from the block's first row and does not check the others
  * (that is the caller's contract); layers with an arbitrary act-order g_idx
