@@ -46,8 +46,24 @@ def is_stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False, extra_flags=()) -> str:
+    """Build if needed.  Safe when several processes (the ranks of one job) import the package at once: the build
+    runs under an exclusive file lock, and a process that waited for the lock finds the library fresh and returns."""
     if not force and not is_stale():
         return LIB_PATH
+    import fcntl
+    obj_dir = os.path.join(HERE, "build")
+    os.makedirs(obj_dir, exist_ok=True)
+    with open(os.path.join(obj_dir, ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not is_stale():
+                return LIB_PATH
+            return _build_locked(force, verbose, extra_flags)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool, extra_flags) -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: libb200gptq.so cannot be built on this machine")
@@ -71,12 +87,13 @@ def build(force: bool = False, verbose: bool = False, extra_flags=()) -> str:
             print(out, file=sys.stderr)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src}:\n{out}")
+    tmp = f"{LIB_PATH}.tmp.{os.getpid()}"
     link = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "--shared", "-cudart", "shared",
-            "-o", LIB_PATH + ".tmp", *objs]
+            "-o", tmp, *objs]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")
-    os.replace(LIB_PATH + ".tmp", LIB_PATH)
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 
