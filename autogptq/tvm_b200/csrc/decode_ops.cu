@@ -182,22 +182,26 @@ __device__ __forceinline__ void cluster_sync_all() {
 // new token; every CTA rotates q and the new k itself (the same fp16 arithmetic as rope_cache_kernel), uses the new
 // k and v from shared memory for position pos[0], and the cluster's first CTA writes them into the caches for the
 // steps to come -- rope_cache_kernel + attn_decode_kernel without the launch in between.
-constexpr int kAttnSplit = 4;
-template <int HD, bool STEP>
-__global__ void __launch_bounds__(512)
+//
+// SPLIT CTAs (a cluster) of WARPS warps share one (sequence, head): the launcher picks the pair so that the whole grid
+// is resident at once (128 registers per thread: 16 warps per SM) -- 4 x 16 for a single sequence, down to one CTA
+// of 4 warps per (sequence, head) for a batch.
+template <int HD, bool STEP, int SPLIT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
                    const __half* __restrict__ v_cache, const long long* __restrict__ pos, __half* __restrict__ out,
                    int heads, int max_seq, float scale, const __half* __restrict__ cos_t,
                    const __half* __restrict__ sin_t, int rope, __half* k_write, __half* v_write) {
     // k_write / v_write (STEP): the same caches, for the one row this kernel writes; that row is never read through
     // k_cache / v_cache here (position pos[0] is served from shared memory), so the read-only path stays valid.
-    constexpr int PER = HD / 32, WARPS = 16;
+    constexpr int PER = HD / 32;
+    static_assert(WARPS * 32 >= HD / 2 && WARPS * 32 >= HD, "the prologue takes one thread per element");
     __shared__ __align__(16) __half q_sm[HD];
     __shared__ __align__(16) __half knew_sm[STEP ? HD : 8], vnew_sm[STEP ? HD : 8];
     __shared__ float sm_m[WARPS], sm_l[WARPS], sm_acc[WARPS][HD];
     __shared__ float cta_m, cta_l, cta_acc[HD];   // this CTA's partial result, read by the cluster's first CTA
     pdl_enter();
-    const int split = blockIdx.x % kAttnSplit, head = blockIdx.x / kAttnSplit, b = blockIdx.y;
+    const int split = blockIdx.x % SPLIT, head = blockIdx.x / SPLIT, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long p64 = pos[0];
     if (STEP && (p64 < 0 || p64 >= max_seq)) return;   // a position outside the caches: refused by the whole cluster
@@ -238,7 +242,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
 #pragma unroll
     for (int d = 0; d < PER; ++d) acc[d] = 0.f;
     float m = -INFINITY, l = 0.f;
-    for (int t0 = (warp * kAttnSplit + split) * 32; t0 < L; t0 += WARPS * kAttnSplit * 32) {
+    for (int t0 = (warp * SPLIT + split) * 32; t0 < L; t0 += WARPS * SPLIT * 32) {
         const int t = t0 + lane;
         // ---- score of this lane's position ----
         float dot = -INFINITY;
@@ -323,11 +327,20 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
             cta_acc[lane * PER + d] = v;
         }
     }
+    if constexpr (SPLIT == 1) {
+        __syncwarp();
+        if (warp == 0) {
+#pragma unroll
+            for (int d = 0; d < PER; ++d)
+                out[((size_t)b * heads + head) * HD + lane * PER + d] = __float2half_rn(cta_acc[lane * PER + d] / cta_l);
+        }
+        return;
+    }
     cluster_sync_all();   // every CTA's (cta_m, cta_l, cta_acc) is visible to the cluster
     if (split == 0 && warp == 0) {
-        float pm[kAttnSplit], pl[kAttnSplit], pa[kAttnSplit][PER];
+        float pm[SPLIT], pl[SPLIT], pa[SPLIT][PER];
 #pragma unroll
-        for (int r = 0; r < kAttnSplit; ++r) {   // all remote reads in flight together
+        for (int r = 0; r < SPLIT; ++r) {   // all remote reads in flight together
             pm[r] = ld_cluster_f32(&cta_m, r);
             pl[r] = ld_cluster_f32(&cta_l, r);
 #pragma unroll
@@ -335,10 +348,10 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
         }
         float gm = -INFINITY;
 #pragma unroll
-        for (int r = 0; r < kAttnSplit; ++r) gm = fmaxf(gm, pm[r]);
-        float gl = 0.f, wgt[kAttnSplit];
+        for (int r = 0; r < SPLIT; ++r) gm = fmaxf(gm, pm[r]);
+        float gl = 0.f, wgt[SPLIT];
 #pragma unroll
-        for (int r = 0; r < kAttnSplit; ++r) {
+        for (int r = 0; r < SPLIT; ++r) {
             wgt[r] = (pm[r] == -INFINITY) ? 0.f : __expf(pm[r] - gm);
             gl += pl[r] * wgt[r];
         }
@@ -346,7 +359,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
         for (int d = 0; d < PER; ++d) {
             float v = 0.f;
 #pragma unroll
-            for (int r = 0; r < kAttnSplit; ++r) v += pa[r][d] * wgt[r];
+            for (int r = 0; r < SPLIT; ++r) v += pa[r][d] * wgt[r];
             out[((size_t)b * heads + head) * HD + lane * PER + d] = __float2half_rn(v / gl);
         }
     }
@@ -434,6 +447,27 @@ dense_gemv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __
 
 using namespace b200gptq;
 
+namespace {
+// One launch of the attention kernel.  A (sequence, head) gets as many warps as keep the whole grid resident at once:
+// the kernel takes 128 registers per thread, so an SM holds 16 warps.
+template <int HD, bool STEP>
+cudaError_t launch_attention(const __half* q, const __half* k_cache, const __half* v_cache, const long long* pos,
+                             __half* out, int batch, int heads, int max_seq, float scale, const __half* cos_t,
+                             const __half* sin_t, int rope, __half* k_write, __half* v_write, void* stream) {
+    const long long pairs = (long long)batch * heads;
+    const long long warps_each = (16LL * sm_count()) / pairs;
+#define B200GPTQ_ATTN(SPLIT, WARPS)                                                                                    \
+    launch_pdl(attn_decode_kernel<HD, STEP, SPLIT, WARPS>, dim3(heads * SPLIT, batch), dim3(WARPS * 32), 0, stream,    \
+               SPLIT, q, k_cache, v_cache, pos, out, heads, max_seq, scale, cos_t, sin_t, rope, k_write, v_write)
+    if (warps_each >= 64) return B200GPTQ_ATTN(4, 16);
+    if (warps_each >= 32) return B200GPTQ_ATTN(4, 8);
+    if (warps_each >= 16) return B200GPTQ_ATTN(4, 4);
+    if (warps_each >= 8) return B200GPTQ_ATTN(1, 8);
+    return B200GPTQ_ATTN(1, 4);
+#undef B200GPTQ_ATTN
+}
+}  // namespace
+
 extern "C" {
 
 B200GPTQ_API int b200gptq_add_norm(void* x, const void* add, const void* w, const void* beta, void* h, int rows,
@@ -470,15 +504,12 @@ B200GPTQ_API int b200gptq_attn_decode(const void* q, const void* k_cache, const 
     const __half* vh = static_cast<const __half*>(v_cache);
     const long long* ph = static_cast<const long long*>(pos);
     __half* oh = static_cast<__half*>(out);
-    const dim3 grid(heads * kAttnSplit, batch);
-    const __half* none = nullptr;
-    __half* nowrite = nullptr;
     if (hd == 128) {
-        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<128, false>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
-                                     oh, heads, max_seq, scale, none, none, 0, nowrite, nowrite));
+        B200GPTQ_CUDA_TRY((launch_attention<128, false>(qh, kh, vh, ph, oh, batch, heads, max_seq, scale, nullptr, nullptr,
+                                                        0, nullptr, nullptr, stream)));
     } else {
-        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<64, false>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
-                                     oh, heads, max_seq, scale, none, none, 0, nowrite, nowrite));
+        B200GPTQ_CUDA_TRY((launch_attention<64, false>(qh, kh, vh, ph, oh, batch, heads, max_seq, scale, nullptr, nullptr,
+                                                       0, nullptr, nullptr, stream)));
     }
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
@@ -496,15 +527,14 @@ B200GPTQ_API int b200gptq_attn_step(const void* qkv, const void* cos_t, const vo
     const __half* sh = static_cast<const __half*>(sin_t);
     const long long* ph = static_cast<const long long*>(pos);
     __half* oh = static_cast<__half*>(out);
-    const dim3 grid(heads * kAttnSplit, batch);
     if (hd == 128) {
-        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<128, true>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
-                                     oh, heads, max_seq, scale, ch, sh, rope, static_cast<__half*>(k_cache),
-                                     static_cast<__half*>(v_cache)));
+        B200GPTQ_CUDA_TRY((launch_attention<128, true>(qh, kh, vh, ph, oh, batch, heads, max_seq, scale, ch, sh, rope,
+                                                       static_cast<__half*>(k_cache), static_cast<__half*>(v_cache),
+                                                       stream)));
     } else {
-        B200GPTQ_CUDA_TRY(launch_pdl(attn_decode_kernel<64, true>, grid, dim3(512), 0, stream, kAttnSplit, qh, kh, vh, ph,
-                                     oh, heads, max_seq, scale, ch, sh, rope, static_cast<__half*>(k_cache),
-                                     static_cast<__half*>(v_cache)));
+        B200GPTQ_CUDA_TRY((launch_attention<64, true>(qh, kh, vh, ph, oh, batch, heads, max_seq, scale, ch, sh, rope,
+                                                      static_cast<__half*>(k_cache), static_cast<__half*>(v_cache),
+                                                      stream)));
     }
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;

@@ -126,7 +126,26 @@ def test_folded_activation_gives_the_same_tokens(arch, bits, desc_act, batch):
     assert all(folds), "the miniature's FFN layers are expected to take the folded activation"
 
 
-@pytest.mark.parametrize("hd,rope,B,heads,pos", [(128, True, 1, 4, 37), (64, False, 3, 6, 0), (128, True, 2, 3, 255), (64, True, 1, 2, 100)])
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("B,heads,pos", [(1, 8, 200), (2, 30, 200), (4, 30, 97), (8, 30, 255), (16, 24, 130), (3, 5, 0)])
+def test_single_query_attention_matches_fp32_softmax(hd, B, heads, pos):
+    """b200gptq_attn_decode against softmax(q k^T / sqrt(hd)) v in fp32, for every way the launcher divides the work:
+    from a cluster of four 16-warp CTAs per (sequence, head) for one sequence down to one 4-warp CTA for a batch."""
+    max_seq = 256
+    g = torch.Generator().manual_seed(hd + pos + B)
+    q = torch.randn(B, heads * hd, generator=g).half().to(DEV)
+    kc = torch.randn(B, heads, max_seq, hd, generator=g).half().to(DEV)
+    vc = torch.randn(B, heads, max_seq, hd, generator=g).half().to(DEV)
+    p = torch.tensor([pos], dtype=torch.long, device=DEV)
+    got = ops.attn_decode(q, kc, vc, p, torch.empty_like(q), heads, hd)
+    qf = q.float().reshape(B, heads, 1, hd)
+    sc = (qf @ kc[:, :, :pos + 1].float().transpose(2, 3)) / hd ** 0.5
+    want = (torch.softmax(sc, dim=-1) @ vc[:, :, :pos + 1].float()).reshape(B, heads * hd)
+    assert torch.allclose(got.float(), want, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("hd,rope,B,heads,pos", [(128, True, 1, 4, 37), (64, False, 3, 6, 0), (128, True, 2, 3, 255), (64, True, 1, 2, 100),
+                                                 (128, True, 16, 24, 130), (64, True, 8, 30, 70), (128, False, 4, 30, 33), (128, True, 2, 30, 200)])
 def test_attention_step_equals_its_two_kernels(hd, rope, B, heads, pos):
     """b200gptq_attn_step (rotary + cache write + attention in one launch) against b200gptq_rope_cache followed by
     b200gptq_attn_decode: the same caches bit for bit, the same attention output up to the order in which the new
