@@ -1005,6 +1005,37 @@ int max_groups_per_stage(const Plan& p, int group_size) {
 // [1] CTAs per SM that the shared-memory footprint is sized for, [2] cap on ring units, [3] trigger of dependents
 // (1 after the own wait, 2 at entry, 3 once all weights are requested), [4] 1 = gather x from global memory,
 // [5] activation applied to x as it is read (Plan::xact)
+// Clusters of `cluster` CTAs with `smem_bytes` of dynamic shared memory that the device holds at once (0: unknown).
+// Answers are kept per thread: a plan is made once per layer, a direct call asks on every launch.
+int resident_clusters(const void* kernel, int cluster, int smem_bytes) {
+    struct Entry { const void* kernel; int dev, cluster, smem, answer; };
+    thread_local Entry cache[16];
+    thread_local int used = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    for (int i = 0; i < used; ++i)
+        if (cache[i].kernel == kernel && cache[i].dev == dev && cache[i].cluster == cluster && cache[i].smem == smem_bytes)
+            return cache[i].answer;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster * 1024);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+    if (used < 16) cache[used++] = Entry{kernel, dev, cluster, smem_bytes, n};
+    return n;
+}
+
+template <int BITS> const void* kernel_for(bool multi, bool perm, int xact);
+template <int BITS> int set_smem_attr_once();
+
 template <int BITS>
 Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* knobs, int* smem_bytes) {
     Plan p;
@@ -1037,13 +1068,34 @@ Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* kn
     if (p.xfull == 1 && tail < xcopy_bytes) tail = xcopy_bytes;
     const int fixed = xs_total<BITS>(p.stage_units, M) + s_sm_bytes(p.group_box) + z_sm_bytes(p.group_box) +
                       ps_bytes(p.stage_units, M) + tail + 1024;
-    // Footprint: as many CTAs per SM as still let a CTA hold its whole slice (at least two); CTAs of the next launch
-    // of the stream find room beside the running ones and fetch their weights early.
+    // Footprint (CTAs per SM that the shared memory is sized for).  A launch should be resident at once: clusters are
+    // placed inside one GPC, so whether `cgs` clusters of `c` CTAs fit is asked of the occupancy calculator, not
+    // computed from the SM count (36 clusters of 8 do not fit at two CTAs per SM, 36864 x 9216: 73 -> 55 us at
+    // three).  Among footprints with the same number of waves the one with the longer ring wins, then the
+    // smaller one (CTAs of the next launch of the stream find room beside the running ones and fetch their weights
+    // early).
     int fit_per_sm = 0;
     if (knobs && knobs[1] > 0) fit_per_sm = knobs[1];
-    else
-        for (int f = (M == 1 ? 3 : 2); f >= 2 && !fit_per_sm; --f)
-            if (fixed + longest * unit_bytes<BITS>() <= kSmemPerSm / f - kSmemCtaReserve) fit_per_sm = f;
+    else {
+        // (the calculator needs the kernels' shared-memory limit raised first)
+        const void* kernel = set_smem_attr_once<BITS>() == B200GPTQ_OK ? kernel_for<BITS>(M > 1, has_perm, p.xact) : nullptr;
+        int best_waves = 0, best_ring = 0;
+        for (int f = (M == 1 ? 4 : 3); f >= 2; --f) {
+            int r = (kSmemPerSm / f - kSmemCtaReserve - fixed) / unit_bytes<BITS>();
+            if (r > longest) r = longest;
+            if (r > kMaxRing) r = kMaxRing;
+            if (r < 2) continue;
+            const int resident = kernel ? resident_clusters(kernel, c, r * unit_bytes<BITS>() + fixed) : 0;
+            if (resident <= 0) { fit_per_sm = 0; break; }
+            const int waves = (p.cgs + resident - 1) / resident;
+            if (!fit_per_sm || waves < best_waves || (waves == best_waves && r > best_ring)) {
+                fit_per_sm = f; best_waves = waves; best_ring = r;
+            }
+        }
+        if (!fit_per_sm)   // no answer from the calculator: the largest footprint count that holds the whole slice
+            for (int f = (M == 1 ? 3 : 2); f >= 2 && !fit_per_sm; --f)
+                if (fixed + longest * unit_bytes<BITS>() <= kSmemPerSm / f - kSmemCtaReserve) fit_per_sm = f;
+    }
     if (!fit_per_sm) fit_per_sm = 2;
     const int budget = kSmemPerSm / fit_per_sm - kSmemCtaReserve;
     int ring = (budget - fixed) / unit_bytes<BITS>();
