@@ -384,6 +384,57 @@ class GPTQDecoder:
         self.pos.copy_(saved_pos)
         self.tokens.copy_(saved_tok)
 
+    #: work splits :meth:`tune` tries: (K slices per SM that the cluster size aims at, CTAs per SM that the footprint is
+    #: sized for; 0 = the library's choice), ``None`` = the library's defaults for a GEMV on its own
+    TUNINGS = (None, (2, 0), (4, 0), (6, 0), (2, 3))
+
+    def tune(self, steps: int = 12, candidates=TUNINGS) -> dict:
+        """Choose the GEMV work split of each kind of linear layer (qkv, o, up, down) by timing the captured decode
+        step, one kind at a time with the others held.  This is the counterpart of the reference's per-shape tile
+        tables (auto_gptq/nn_modules/tvm_untils/pycuda_warpper.py:77-127), measured in place because the best split
+        depends on the kernels around the GEMV (4-5 % of a Llama-7B step, 2-3 % of an OPT-66B step on one B200).
+        Position and tokens are restored; cache rows past the current position are used as scratch.  With several
+        ranks every rank calls this at the same point and all take the split that is fastest for the slowest rank.
+        Returns {kind: tuning}; a batch of more than 8 rows does not run GEMVs and is left alone."""
+        kinds = ("qkv", "o", "up", "down")
+        chosen = {k: getattr(self.layers[0], k).gemv_tuning for k in kinds}
+        if self.batch > 8 or self._pos_host + steps + 3 > self.cfg.max_seq:
+            return chosen
+        dev = self.device
+
+        def apply(kind, tuning):
+            for L in self.layers:
+                getattr(L, kind).gemv_tuning = tuning
+
+        def step_ms() -> float:
+            self.capture()
+            saved = (self.pos.clone(), self.tokens.clone(), self._pos_host)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            e0.record()
+            self.decode(steps)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            self.pos.copy_(saved[0])
+            self.tokens.copy_(saved[1])
+            self._pos_host = saved[2]
+            t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+            if self.world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            return float(t.item())
+
+        for kind in kinds:
+            if not isinstance(getattr(self.layers[0], kind), QuantLinear):
+                continue
+            times = []
+            for cand in candidates:
+                apply(kind, cand)
+                times.append(step_ms())
+            chosen[kind] = candidates[times.index(min(times))]
+            apply(kind, chosen[kind])
+        self.capture()
+        return chosen
+
     def decode(self, steps: int) -> torch.Tensor:
         check_positions(self._pos_host, steps, self.cfg.max_seq)
         self._pos_host += steps

@@ -271,6 +271,8 @@ def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
     e1.record()
     torch.cuda.synchronize()
     prefill_ms = e0.elapsed_time(e1)
+    # load-time tuning, outside the timed region: the GEMV work split per kind of linear layer, measured in the step
+    tuning = m.tune()
     m.capture()
     torch.cuda.synchronize()
     if world > 1:
@@ -292,7 +294,7 @@ def time_decode(dev, world, cfg, name, batch, prompt_len, decode_steps):
            "ms_per_token": ms / decode_steps, "prefill_ms": prefill_ms,
            "weight_bytes_per_token_per_gpu": m.bytes_per_token(),
            "frac_of_hbm_roofline": m.bytes_per_token() / per_tok_s / 1e9 / peak,
-           "last_token": int(toks[-1, 0]),
+           "last_token": int(toks[-1, 0]), "gemv_tuning": {k: (list(v) if v else None) for k, v in tuning.items()},
            "allreduce": "none" if world == 1 else ("fused peer-memory exchange" if batch <= 8 else "process group")}
     if m.exchange is not None:
         out["exchange_status"] = m.exchange.status()     # 0: no wait of the fused all-reduce ever ran out

@@ -30,6 +30,29 @@ def test_graph_decode_equals_eager_decode(arch, bits, desc_act):
     assert int(b.pos) == 12 + 6
 
 
+@pytest.mark.parametrize("arch,bits,desc_act", [("llama", 4, False), ("opt", 3, True)])
+def test_tuning_in_place_keeps_the_state_and_the_result(arch, bits, desc_act):
+    """GPTQDecoder.tune(): every kind of linear gets one of the candidate work splits, position and tokens are as
+    before, and the logits of the next step stay within the output contract of the untuned decoder's (a different
+    split of K changes the order of the fp32 sums only)."""
+    cfg = _small(arch, bits, desc_act)
+    prompt = torch.randint(0, cfg.vocab, (1, 12), generator=torch.Generator().manual_seed(1)).to(DEV)
+    ref = decoder.GPTQDecoder(cfg, batch=1, device=DEV)
+    ref.prefill(prompt)
+    ref.decode(1)
+    m = decoder.GPTQDecoder(cfg, batch=1, device=DEV)
+    m.prefill(prompt)
+    pos, tok = int(m.pos), m.tokens.clone()
+    chosen = m.tune(steps=4)
+    assert set(chosen) == {"qkv", "o", "up", "down"} and all(c in m.TUNINGS for c in chosen.values())
+    assert int(m.pos) == pos and torch.equal(m.tokens, tok) and m._pos_host == pos
+    for L in m.layers:
+        assert L.qkv.gemv_tuning == chosen["qkv"] and L.down.gemv_tuning == chosen["down"]
+    m.decode(1)
+    assert torch.allclose(m.last_logits.float(), ref.last_logits.float(), rtol=0, atol=2e-2)
+    ops.check_status(DEV)
+
+
 class _Dense(torch.nn.Module):
     """Stand-in for a QuantLinear that multiplies by the dequantised fp16 weights with torch."""
 
