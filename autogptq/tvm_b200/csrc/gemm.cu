@@ -29,6 +29,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -50,7 +51,10 @@ constexpr int kTmemAColsPerStage = 32;  // 64 k x fp16 = 32 columns of 32 bits
 constexpr int kSmemBudget = 222 * 1024;  // ring bytes; the opt-in maximum per CTA is 227 KB
 constexpr int kStatusWord = kMaxCounters - 1;  // sticky error word inside the counter region
 constexpr int kMaxSplits = 4;            // CTAs that share the k-tiles of one output tile (split K)
-constexpr int kGroups = 3;               // weight groups of the launched kernel
+constexpr int kGroups = 3;               // weight groups of the launched kernel (one CTA per SM)
+// two CTAs on an SM share what bounds a k-tile (its k-tiles count 19/10): the second CTA pays only where it
+// fills a half-empty wave or halves the k-tiles of a CTA
+constexpr int kTwoPerSmPenaltyNum = 19, kTwoPerSmPenaltyDen = 10;
 
 // 3-bit: order in which the 32 fields of a row block leave the 7-window unpack (pairs are
 // adjacent entries).  x is permuted the same way by the pre-pass.
@@ -230,7 +234,7 @@ prep_x_kernel(const __half* __restrict__ x, const int32_t* __restrict__ x_perm, 
 }
 
 template <int BITS, int kWeightGroups>
-__global__ void __launch_bounds__(gemm_threads(kWeightGroups), 1)
+__global__ void __launch_bounds__(gemm_threads(kWeightGroups), kWeightGroups == 1 ? 2 : 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const int32_t* __restrict__ qzeros, const __half* __restrict__ scales,
             const int32_t* __restrict__ g_idx, const __half* __restrict__ bias, __half* __restrict__ y, int M, int K,
@@ -380,13 +384,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         for (int kt = wgroup; kt < KT; kt += kWeightGroups) {
             const int rb = 2 * (kt_first + kt) + kh;
             // fetch the scale / zero-point of this thread's next k-tile now, a whole iteration ahead of their use
-            constexpr int kRbStep = 2 * kWeightGroups;
-            if (rb + kRbStep < RB && col_ok) {
+            const int rb_nxt = rb + 2 * kWeightGroups;
+            if (rb_nxt < RB && col_ok) {
                 if (tab_groups) {
-                    load_group(rb + kRbStep, g_nxt, s_nxt, z_nxt);
+                    load_group(rb_nxt, g_nxt, s_nxt, z_nxt);
                 } else {
-                    const int gn = group_of(rb + kRbStep);
-                    if (gn != g_cur) load_group(rb + kRbStep, g_nxt, s_nxt, z_nxt);
+                    const int gn = group_of(rb_nxt);
+                    if (gn != g_cur) load_group(rb_nxt, g_nxt, s_nxt, z_nxt);
                     else { g_nxt = g_cur; s_nxt = s_cur; z_nxt = z_cur; }
                 }
             }
@@ -522,26 +526,37 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Split K: with few rows of x a tile's time is the chain of hand-overs per k-tile, not its arithmetic, and a layer
-// with fewer than #SM / 2 column tiles leaves SMs idle; the k-tiles of a tile are then spread over as many CTAs as
-// there are idle SMs per tile (up to kMaxSplits).  Only for one row tile (M <= 128) and when every split keeps at
-// least 16 k-tiles (40 above 64 rows).  (Two split CTAs per SM were measured too, with two weight groups and half of the shared and
-// tensor memory each: 37.7 us against 33.5 us for 16 rows of the 4096 x 12288 layer -- what bounds a k-tile is shared
-// by the CTAs of an SM -- so a split never puts two CTAs on one SM.)
-int pick_splits(int M, int N, int K) {
-    if (M > 128) return 1;
-    const int tiles = (N + BN - 1) / BN;
-    if (tiles >= kMaxCounters - 1) return 1;
-    int sp = sm_count() / tiles;
+// Work split of a launch.  With few rows of x a tile's time is the chain of hand-overs per k-tile, not its arithmetic:
+// the time of a launch is (waves of CTAs) x (k-tiles per CTA).  Two things shorten it.  Split K: the k-tiles of a
+// column tile are spread over up to kMaxSplits CTAs (blockIdx.z), only for one row tile (M <= 128) and when every
+// run keeps at least 16 k-tiles (40 above 64 rows: taller partial sums).  Two CTAs per SM (M <= 64): one group of
+// weight warps instead of three (320 threads, so that two CTAs fit the register file) and half of the shared and
+// tensor memory each.  An SM works through k-tiles at about the same rate either way (0.4-0.5 us per k-tile), so the
+// second CTA is taken only where it fills a half-empty second wave or halves the k-tiles of a CTA: 16 rows,
+// 4096 x 12288 33.1 -> 29.5 us, 4096 x 22016 64.5 -> 48.5 us, 9216 x 27648 (3-bit) 141 -> 114 us.
+struct GemmSplit { int splits, per_sm; };
+int splits_for(int M, int tiles, int KT, int slots) {
+    if (M > 128 || tiles >= kMaxCounters - 1) return 1;
+    int sp = slots / tiles;
     if (sp > kMaxSplits) sp = kMaxSplits;
-    const int KT = (K + BK - 1) / BK;
-    // every split keeps enough k-tiles to pay for its own start-up and for the final sum (more with taller tiles,
-    // whose partial sums are larger): measured on 4096 x 4096, 16 rows 33.5 -> 26 us with four splits, 128 rows
-    // 34.6 -> 37.4 us with two
+    // every run keeps enough k-tiles to pay for its own start-up and for the final sum: measured on 4096 x 4096,
+    // 16 rows 33.5 -> 21 us with four runs, 128 rows 34.6 -> 37.4 us with two
     const int min_tiles = M <= 64 ? 16 : 40;
     while (sp > 1 && KT / sp < min_tiles) --sp;
     return sp < 1 ? 1 : sp;
 }
+GemmSplit pick_split(int M, int N, int K) {
+    const int tiles = (N + BN - 1) / BN, KT = (K + BK - 1) / BK, sms = sm_count();
+    GemmSplit one = {splits_for(M, tiles, KT, sms), 1};
+    if (M > 64) return one;
+    GemmSplit two = {splits_for(M, tiles, KT, 2 * sms), 2};
+    auto cost = [&](const GemmSplit& g) {
+        const long long ctas = (long long)tiles * g.splits, slots = (long long)sms * g.per_sm;
+        return ((ctas + slots - 1) / slots) * ((KT + g.splits - 1) / g.splits);
+    };
+    return cost(two) * kTwoPerSmPenaltyNum < cost(one) * kTwoPerSmPenaltyDen ? two : one;
+}
+int pick_splits(int M, int N, int K) { return pick_split(M, N, K).splits; }
 size_t split_partial_bytes(int M, int N, int K) {
     const int sp = pick_splits(M, N, K);
     if (sp == 1) return 0;
@@ -568,9 +583,10 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
     // scale / zero-point table of the CTA's columns for every group, if it leaves room for >= 4 stages
     const int gs_eff = group_size;
     const int G = (K + gs_eff - 1) / gs_eff;
-    const int splits = pick_splits(M, N, K);
-    const int smem_budget = kSmemBudget;
-    const int tmem_cols = kTmemCols;
+    const GemmSplit split = pick_split(M, N, K);
+    const int splits = split.splits;
+    const int smem_budget = split.per_sm == 2 ? kSmemBudget / 2 - 2048 : kSmemBudget;
+    const int tmem_cols = kTmemCols / split.per_sm;
     int tab_bytes = G * BN * 4 + ((K / 32 * 2 + 15) / 16) * 16;
     int tab_groups = G;
     if (G > 65535 || smem_budget - tab_bytes < 4 * stage_bytes) { tab_bytes = 0; tab_groups = 0; }
@@ -605,21 +621,27 @@ int launch_gemm(const __half* x_for_tma, const int32_t* qweight, const int32_t* 
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)cudaErrorInvalidValue); return B200GPTQ_ERR_CUDA; }
     }
 
-    // the shared-memory opt-in is set once per device and bit width; afterwards the launch path only reads
-    static std::once_flag attr_once[64];
-    static int attr_result[64];
-    int dev = 0;
-    B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return B200GPTQ_ERR_TOO_LARGE;
-    std::call_once(attr_once[dev], [dev] {
-        attr_result[dev] = (int)cudaFuncSetAttribute(gemm_kernel<BITS, kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     226 * 1024);
-    });
-    if (attr_result[dev] != 0) { set_last_cuda_error(attr_result[dev]); return B200GPTQ_ERR_CUDA; }
     dim3 grid((M + TN - 1) / TN, (N + BN - 1) / BN, splits);
-    gemm_kernel<BITS, kGroups><<<grid, gemm_threads(kGroups), smem_bytes, stream>>>(
-        tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N, group_size, TN, S, tab_groups, a_off, status, splits,
-        tmem_cols, partial);
+    auto launch = [&](auto groups) -> int {
+        constexpr int kG = decltype(groups)::value;
+        // the shared-memory opt-in is set once per device and instantiation; afterwards the launch path only reads
+        static std::once_flag attr_once[64];
+        static int attr_result[64];
+        int dev = 0;
+        B200GPTQ_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) return B200GPTQ_ERR_TOO_LARGE;
+        std::call_once(attr_once[dev], [dev] {
+            attr_result[dev] = (int)cudaFuncSetAttribute(gemm_kernel<BITS, kG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                         226 * 1024);
+        });
+        if (attr_result[dev] != 0) { set_last_cuda_error(attr_result[dev]); return B200GPTQ_ERR_CUDA; }
+        gemm_kernel<BITS, kG><<<grid, gemm_threads(kG), smem_bytes, stream>>>(
+            tmap_x, tmap_w, qzeros, scales, g_idx, bias, y, M, K, N, group_size, TN, S, tab_groups, a_off, status, splits,
+            tmem_cols, partial);
+        return B200GPTQ_OK;
+    };
+    const int st = split.per_sm == 2 ? launch(std::integral_constant<int, 1>{}) : launch(std::integral_constant<int, kGroups>{});
+    if (st != B200GPTQ_OK) return st;
     B200GPTQ_CUDA_TRY(cudaGetLastError());
     return B200GPTQ_OK;
 }

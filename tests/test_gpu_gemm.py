@@ -42,6 +42,8 @@ GEMM_CASES = [
     (3, 4096, 512, 128, 200, False),
     (3, 352, 96, -1, 33, False),
     (4, 512, 128, 128, 1, False),        # works for any M >= 1
+    (3, 2048, 19200, 128, 16, True),     # 150 column tiles: two CTAs (one group of weight warps each) per SM
+    (4, 1024, 19200, 64, 40, False),     # the same with a 64-row tile of x
 ]
 
 
