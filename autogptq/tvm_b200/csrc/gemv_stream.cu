@@ -1056,12 +1056,13 @@ Plan make_plan(int M, int K, int N, int group_size, bool has_perm, const int* kn
     p.push = (c > 1 && red_bytes(M, c) <= kMaxRedBytes) ? 1 : 0;
     p.early = (knobs && knobs[3] > 0) ? knobs[3] - 1 : 0;
     p.xact = knobs ? knobs[5] : 0;
-    // layers with a gather take x through a linear bulk copy when it is small enough (knobs[4] == 1 switches it
-    // off): small copies get bytes of their own, larger ones share the bytes of the partial sums (the CTA then joins
-    // its cluster's barrier only when it has finished with x).  Without a gather a CTA reads only its own rows of x,
-    // and plain loads measured faster than the copy.
+    // layers with a gather, and several rows of x, take x through linear bulk copies when it is small enough
+    // (knobs[4] == 1 switches it off): small copies get bytes of their own, larger ones share the bytes of the partial
+    // sums (the CTA then joins its cluster's barrier only when it has finished with x).  One row without a gather: a
+    // CTA reads only its own rows of x, and plain loads measured faster than the copy; with M rows the 2-byte loads
+    // of all CTAs queue up at the same L2 lines (8 rows of a 4096 x 12288 layer: 27 us with loads).
     const int xcopy_bytes = M * (has_perm ? K : longest * kUnitRows) * 2;
-    p.xfull = (!has_perm || (knobs && knobs[4] == 1)) ? 0 : (xcopy_bytes <= 4096 ? 2 : (xcopy_bytes <= kXFullMax ? 1 : 0));
+    p.xfull = ((!has_perm && M == 1) || (knobs && knobs[4] == 1)) ? 0 : (xcopy_bytes <= 4096 ? 2 : (xcopy_bytes <= kXFullMax ? 1 : 0));
     if (p.xact == 1) p.xfull = 0;   // gate and up are two runs of the row: no single copy (callers fuse SwiGLU only without a gather)
     int tail = part_bytes(M) + (p.push ? red_bytes(M, c) : 0);
     if (p.xfull == 2) tail += xcopy_bytes;
