@@ -84,7 +84,7 @@ def _to_module(layer: synth.PackedLayer, device) -> QuantLinear:
         # rows re-ordered by group and back to k // group_size: keep only the re-ordered copy of the weights
         m.qweight = m._qweight_run
         m.g_idx = (torch.arange(layer.K, device=device) // m.groupsize).to(torch.int32)
-        m._ready_for = (m.qweight.device, m.qweight.data_ptr(), m.g_idx.data_ptr())
+        m._ready_for = (m.qweight.data_ptr(), m.g_idx.data_ptr())
     return m
 
 

@@ -161,10 +161,11 @@ class QuantLinear(nn.Module):
             b = g_run.view(K // 32, 32)
             self._gemm_ok = self.bits in (3, 4) and bool((b == b[:, :1]).all().item())
         self._plans = {}
-        self._ready_for = (dev, self.qweight.data_ptr(), self.g_idx.data_ptr())
+        self._ready_for = (self.qweight.data_ptr(), self.g_idx.data_ptr())
 
     def _ready(self) -> bool:
-        return self._ready_for == (self.qweight.device, self.qweight.data_ptr(), self.g_idx.data_ptr())
+        b = self._buffers    # (a tensor on another device has another address, so the addresses say it all)
+        return self._ready_for == (b["qweight"].data_ptr(), b["g_idx"].data_ptr())
 
     # ---- forward --------------------------------------------------------------------------
     def forward(self, x):
@@ -181,6 +182,14 @@ class QuantLinear(nn.Module):
             raise RuntimeError("QuantLinear.forward needs CUDA tensors: this backend has no CPU path")
         if not self._ready():
             self.post_init()
+        # decode: up to 8 rows, already fp16 and contiguous, a plan at hand -- one allocation and one library call
+        if x.dtype is torch.float16 and x.is_contiguous() and x.shape[-1] == self.infeatures:
+            M = x.numel() // self.infeatures
+            if 0 < M <= GEMV_MAX_M:
+                plan = self._plans.get((M, self.gemv_tuning))
+                if (plan is not None and plan._keep[5] is self._buffers.get("bias", self.__dict__.get("bias"))
+                        and x.get_device() == plan._index):
+                    return plan.launch(x, x.shape[:-1] + (self.outfeatures,))
         out_shape = x.shape[:-1] + (self.outfeatures,)
         x2 = x.half().reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
