@@ -346,25 +346,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         uint32_t* tab = reinterpret_cast<uint32_t*>(base_ptr + (size_t)S * stage_bytes);
         uint16_t* gmap = reinterpret_cast<uint16_t*>(tab + (size_t)tab_groups * BN);
         auto group_of = [&](int rb) { return g_idx ? __ldg(g_idx + 32 * rb) : (32 * rb) / group_size; };
+        // The table holds the groups this CTA's k-tiles can touch: with the trivial g_idx that is a contiguous run
+        // (a split-K CTA needs a fraction of the layer's groups); a stored g_idx may name any group.
+        const int rb_first = 2 * kt_first, rb_end = min(RB, 2 * (kt_first + KT));
+        const int g_first = (tab_groups && !g_idx) ? (32 * rb_first) / group_size : 0;
+        const int g_count = !tab_groups ? 0 : (g_idx ? tab_groups : (32 * rb_end - 1) / group_size - g_first + 1);
         if (tab_groups) {
-            const int pt = threadIdx.x - 32;   // 0 .. 511
-            for (int i = pt; i < tab_groups * BN; i += kWeightWarps * kWeightGroups * 32) {
-                const int g = i / BN, c = i % BN;
-                uint32_t e = 0;
-                if (n0 + c < N) {
-                    const uint32_t sc = __half_as_ushort(scales[(size_t)g * N + n0 + c]);
-                    const uint32_t z = (uint32_t)zero_point<BITS>(qzeros + (size_t)g * zwords, n0 + c);
-                    e = sc | (z << 16);
+            constexpr int kFillThreads = kWeightWarps * kWeightGroups * 32;
+            const int pt = threadIdx.x - 32;   // 0 .. kFillThreads - 1
+            const int total = g_count * BN;
+            // four entries per thread and pass, their global loads issued together (one entry at a time the fill
+            // was a chain of 16 memory round trips per thread, a third of a 16-row launch)
+#pragma unroll 1
+            for (int i0 = pt; i0 < total; i0 += 4 * kFillThreads) {
+                uint32_t sc[4];
+                int z[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * kFillThreads;
+                    const int g = g_first + i / BN, c = i % BN;
+                    sc[j] = 0u; z[j] = 0;
+                    if (i < total && n0 + c < N) {
+                        sc[j] = __half_as_ushort(__ldg(scales + (size_t)g * N + n0 + c));
+                        z[j] = zero_point<BITS>(qzeros + (size_t)g * zwords, n0 + c);
+                    }
                 }
-                tab[i] = e;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * kFillThreads;
+                    if (i < total) tab[i] = sc[j] | ((uint32_t)z[j] << 16);
+                }
             }
-            for (int rb = pt; rb < RB; rb += kWeightWarps * kWeightGroups * 32) gmap[rb] = (uint16_t)group_of(rb);
-            asm volatile("bar.sync 1, %0;" ::"n"(kWeightWarps * kWeightGroups * 32) : "memory");
+            for (int rb = rb_first + pt; rb < rb_end; rb += kFillThreads)
+                gmap[rb - rb_first] = (uint16_t)(group_of(rb) - g_first);
+            asm volatile("bar.sync 1, %0;" ::"n"(kFillThreads) : "memory");
         }
         auto load_group = [&](int rb, int& g, __half& sc, int& z) {
-            if (col_ok && rb < RB) {
+            if (col_ok && rb < rb_end) {
                 if (tab_groups) {
-                    g = gmap[rb];
+                    g = gmap[rb - rb_first];
                     const uint32_t e = tab[g * BN + col];
                     sc = __ushort_as_half((unsigned short)(e & 0xffffu));
                     z = (int)(e >> 16);
@@ -385,7 +405,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             const int rb = 2 * (kt_first + kt) + kh;
             // fetch the scale / zero-point of this thread's next k-tile now, a whole iteration ahead of their use
             const int rb_nxt = rb + 2 * kWeightGroups;
-            if (rb_nxt < RB && col_ok) {
+            if (rb_nxt < rb_end && col_ok) {
                 if (tab_groups) {
                     load_group(rb_nxt, g_nxt, s_nxt, z_nxt);
                 } else {
