@@ -504,7 +504,7 @@ def main():
             par = tp_parity_llama(dev)
             if rank == 0:
                 extras["llama7b_decode"]["tp_parity"] = par
-        # config 4 rides on the same line; on one GPU only while the run is still within its time budget
+        # config 4 rides on the same line; on one GPU only while the run has taken less than 300 s so far
         if not args.no_opt66b and (world > 1 or time.perf_counter() - t_program < 300.0):
             torch.cuda.empty_cache()
             barrier()
