@@ -56,6 +56,9 @@ _SIGNATURES = {
     "b200gptq_attn_step": (_c_int, [_c_void_p] * 7 + [_c_int] * 5 + [ctypes.c_float, _c_void_p]),
     "b200gptq_act": (_c_int, [_c_void_p] * 2 + [_c_int] * 3 + [_c_void_p]),
     "b200gptq_dense_gemv": (_c_int, [_c_void_p] * 3 + [_c_int] * 3 + [_c_void_p]),
+    "b200gptq_pick_local": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, ctypes.c_longlong, _c_int, _c_int, _c_void_p,
+                                     _c_void_p, ctypes.c_longlong, _c_void_p, _c_void_p]),
+    "b200gptq_pick_final": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_void_p]),
 }
 
 

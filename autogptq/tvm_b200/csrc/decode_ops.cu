@@ -442,6 +442,86 @@ dense_gemv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __
     }
 }
 
+// Greedy pick, first half: the largest of one row's logits (the lowest column on a tie, like the framework's argmax)
+// over columns [0, valid).  One rank: the token goes straight to `tokens[row]`.  Several ranks: the row's slots of the
+// exchange vector are written -- {logit, 0, index / 256, index % 256} as fp16 (all exact) in this rank's four slots,
+// zeros in the others, so that the sum over ranks is a gather.
+__global__ void __launch_bounds__(1024)
+pick_local_kernel(const __half* __restrict__ logits, int ld, int valid, long long base_index, int world, int rank,
+                  __half* __restrict__ slots, long long* __restrict__ tokens, long long max_token,
+                  long long* __restrict__ pos_inc) {
+    pdl_enter();
+    __shared__ float sm_v[32];
+    __shared__ int sm_i[32];
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const __half* lr = logits + (size_t)row * ld;
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int c0 = threadIdx.x * 8; c0 < valid; c0 += 1024 * 8) {   // ld % 8 == 0: whole 16-byte pieces
+        const uint4 raw = *reinterpret_cast<const uint4*>(lr + c0);
+        const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float v = __half2float(h[i]);
+            if (c0 + i < valid && (v > best || at == 0x7fffffff)) { best = v; at = c0 + i; }
+        }
+    }
+    auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, best, o);
+        const int i = __shfl_xor_sync(0xffffffffu, at, o);
+        if (i != 0x7fffffff && (at == 0x7fffffff || better(v, i, best, at))) { best = v; at = i; }
+    }
+    if (lane == 0) { sm_v[warp] = best; sm_i[warp] = at; }
+    __syncthreads();
+    if (warp == 0) {
+        best = sm_v[lane]; at = sm_i[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float v = __shfl_xor_sync(0xffffffffu, best, o);
+            const int i = __shfl_xor_sync(0xffffffffu, at, o);
+            if (i != 0x7fffffff && (at == 0x7fffffff || better(v, i, best, at))) { best = v; at = i; }
+        }
+        const long long token = base_index + (at == 0x7fffffff ? 0 : at);
+        if (world == 1) {
+            if (lane == 0) tokens[row] = token < max_token ? token : max_token;
+        } else {
+            for (int j = lane; j < 4 * world; j += 32) {
+                float v = 0.f;
+                if (j == 4 * rank) v = best;
+                if (j == 4 * rank + 2) v = (float)(token >> 8);
+                if (j == 4 * rank + 3) v = (float)(token & 255);
+                slots[(size_t)row * 4 * world + j] = __float2half_rn(v);
+            }
+        }
+        if (lane == 0 && row == 0 && pos_inc) *pos_inc += 1;
+    }
+}
+
+// Second half (several ranks): the summed slots hold every rank's {logit, 0, index / 256, index % 256}; the best logit
+// wins, the lowest rank on a tie (its columns come first).
+__global__ void __launch_bounds__(32)
+pick_final_kernel(const __half* __restrict__ slots, int world, long long* __restrict__ tokens, long long max_token,
+                  long long* __restrict__ pos_inc) {
+    pdl_enter();
+    const int row = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const __half* s = slots + (size_t)row * 4 * world;
+        float best = -INFINITY;
+        long long token = 0;
+        for (int r = 0; r < world; ++r) {
+            const float v = __half2float(s[4 * r]) + __half2float(s[4 * r + 1]);
+            if (r == 0 || v > best) {
+                best = v;
+                token = (long long)__half2float(s[4 * r + 2]) * 256 + (long long)__half2float(s[4 * r + 3]);
+            }
+        }
+        tokens[row] = token < max_token ? token : max_token;
+        if (row == 0 && pos_inc) *pos_inc += 1;
+    }
+}
+
 }  // namespace
 }  // namespace b200gptq
 
@@ -579,6 +659,28 @@ B200GPTQ_API int b200gptq_dense_gemv(const void* x, const void* w, void* y, int 
             });
         B200GPTQ_CUDA_TRY(launch_pdl(dense_gemv_kernel<8>, dim3(blocks), dim3(256), smem, stream, 1, xh, wh, yh, rows, K, N));
     }
+    return B200GPTQ_OK;
+}
+
+B200GPTQ_API int b200gptq_pick_local(const void* logits, int rows, int ld, int valid, long long base_index, int world,
+                                     int rank, void* slots, long long* tokens, long long max_token, long long* pos_inc,
+                                     void* stream) {
+    if (!logits || (world == 1 ? !tokens : !slots)) return B200GPTQ_ERR_NULL_POINTER;
+    if (rows < 1 || ld < 8 || ld % 8 != 0 || valid < 1 || valid > ld || world < 1 || rank < 0 || rank >= world)
+        return B200GPTQ_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(logits) & 15u) return B200GPTQ_ERR_ALIGNMENT;
+    B200GPTQ_CUDA_TRY(launch_pdl(pick_local_kernel, dim3(rows), dim3(1024), 0, stream, 1,
+                                 static_cast<const __half*>(logits), ld, valid, base_index, world, rank,
+                                 static_cast<__half*>(slots), tokens, max_token, pos_inc));
+    return B200GPTQ_OK;
+}
+
+B200GPTQ_API int b200gptq_pick_final(const void* slots, int rows, int world, long long* tokens, long long max_token,
+                                     long long* pos_inc, void* stream) {
+    if (!slots || !tokens) return B200GPTQ_ERR_NULL_POINTER;
+    if (rows < 1 || world < 1) return B200GPTQ_ERR_SHAPE;
+    B200GPTQ_CUDA_TRY(launch_pdl(pick_final_kernel, dim3(rows), dim3(32), 0, stream, 1,
+                                 static_cast<const __half*>(slots), world, tokens, max_token, pos_inc));
     return B200GPTQ_OK;
 }
 

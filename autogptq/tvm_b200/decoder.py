@@ -364,8 +364,23 @@ class GPTQDecoder:
         ops.add_norm(x, delta, self.final_norm_w, self.final_norm_b, h, eps, rms)
         self.last_hidden = h
         logits = self._project(h)
-        self.tokens.copy_(self._pick(logits))
-        self.pos.add_(1)
+        if (logits.dtype is torch.float16 and logits.is_contiguous()
+                and (self.world == 1 or (self.exchange is not None and B <= 8))):   # the exchange takes up to 8 rows
+            # greedy pick and the step's position in the library's kernels: one launch on one GPU, two around the
+            # exchange on several (the framework's route is a dozen element-wise launches)
+            self.last_logits = logits
+            valid = min(self.vocab_local, self.cfg.vocab - self.rank * self.vocab_local)
+            top = self.cfg.vocab - 1
+            if self.world == 1:
+                ops.pick_local(logits, valid, 0, 1, 0, None, self.tokens, top, self.pos)
+            else:
+                slots = torch.empty((B, 4 * self.world), dtype=torch.float16, device=self.device)
+                ops.pick_local(logits, valid, self.rank * self.vocab_local, self.world, self.rank, slots, None, top)
+                ops.tp_allreduce(slots, self.exchange)
+                ops.pick_final(slots, self.world, self.tokens, top, self.pos)
+        else:
+            self.tokens.copy_(self._pick(logits))
+            self.pos.add_(1)
 
     def capture(self):
         """Warm up (allocates scratch, builds run-time views) and capture one decode step in a CUDA graph."""
@@ -485,7 +500,7 @@ class GPTQDecoder:
             parts = [torch.empty_like(lg) for _ in range(self.world)]
             dist.all_gather(parts, lg.contiguous(), group=self.group)
             lg = torch.cat(parts, dim=1)
-        return lg[:, :self.cfg.vocab]
+        return lg[:, :self.cfg.vocab].float()
 
     def bytes_per_token(self) -> int:
         """Bytes of weights this rank streams per decode step (packed linears + its lm_head slice)."""

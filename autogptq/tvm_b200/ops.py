@@ -360,6 +360,25 @@ def attn_decode(q, k_cache, v_cache, pos, out, heads: int, hd: int):
     return out
 
 
+def pick_local(logits, valid: int, base_index: int, world: int, rank: int, slots, tokens, max_token: int, pos_inc=None):
+    """``b200gptq_pick_local``: greedy pick over this rank's fp16 ``logits[rows, ld]`` (columns ``[0, valid)``)."""
+    _need_cuda("logits", logits, torch.float16)
+    rows, ld = logits.shape
+    with torch.cuda.device(logits.device):
+        st = _lib.lib.b200gptq_pick_local(_ptr(logits), rows, ld, valid, base_index, world, rank, _ptr(slots),
+                                          _ptr(tokens), max_token, _ptr(pos_inc), _stream(logits.device))
+    _lib.check(st, "b200gptq_pick_local")
+
+
+def pick_final(slots, world: int, tokens, max_token: int, pos_inc=None):
+    """``b200gptq_pick_final``: the winning rank's token per row from the summed ``slots[rows, 4 * world]``."""
+    _need_cuda("slots", slots, torch.float16)
+    with torch.cuda.device(slots.device):
+        st = _lib.lib.b200gptq_pick_final(_ptr(slots), slots.shape[0], world, _ptr(tokens), max_token, _ptr(pos_inc),
+                                          _stream(slots.device))
+    _lib.check(st, "b200gptq_pick_final")
+
+
 def attn_step(qkv, cos_t, sin_t, pos, k_cache, v_cache, out, heads: int, hd: int, rope: bool):
     """:func:`rope_cache` and :func:`attn_decode` as one launch (``b200gptq_attn_step``): ``qkv`` ``[B, 3*heads*hd]`` of
     the new token in, attention output ``[B, heads*hd]`` out, caches updated at position ``pos[0]``."""

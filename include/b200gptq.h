@@ -362,6 +362,26 @@ B200GPTQ_API int b200gptq_act(const void* u, void* act, int rows, int I, int gat
  */
 B200GPTQ_API int b200gptq_dense_gemv(const void* x, const void* w, void* y, int rows, int K, int N, void* stream);
 
+/*
+ * Greedy token pick of a decode step (the reference leaves it to transformers' generate(),
+ * end2end/autogptq-generation-inference-benchmark.py:26-49; here it is one launch on one GPU and two around the
+ * exchange on several, instead of a dozen element-wise kernels).
+ *
+ *   b200gptq_pick_local  per row of fp16 logits[rows, ld]: the largest of columns [0, valid) (lowest column on a tie).
+ *                        world == 1: tokens[row] = min(base_index + column, max_token).
+ *                        world > 1 : slots[row, 4*world] (fp16) gets {logit, 0, token / 256, token % 256} in this rank's
+ *                        four entries and zeros elsewhere; the caller sums `slots` over the ranks
+ *                        (b200gptq_tp_allreduce) and calls b200gptq_pick_final.
+ *   b200gptq_pick_final  tokens[row] = the token of the rank with the largest logit (lowest rank on a tie), clamped.
+ * pos_inc (nullable): a device int64 that the launch increments by one (the step's position), so that a captured
+ * graph advances it.  ld % 8 == 0, logits 16-byte aligned.
+ */
+B200GPTQ_API int b200gptq_pick_local(const void* logits, int rows, int ld, int valid, long long base_index, int world,
+                                     int rank, void* slots, long long* tokens, long long max_token, long long* pos_inc,
+                                     void* stream);
+B200GPTQ_API int b200gptq_pick_final(const void* slots, int rows, int world, long long* tokens, long long max_token,
+                                     long long* pos_inc, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -149,6 +149,36 @@ def test_folded_activation_gives_the_same_tokens(arch, bits, desc_act, batch):
     assert all(folds), "the miniature's FFN layers are expected to take the folded activation"
 
 
+@pytest.mark.parametrize("rows,ld,valid", [(1, 32000, 32000), (3, 4000, 3997), (16, 1000, 1000), (2, 8, 5)])
+def test_greedy_pick_matches_argmax(rows, ld, valid):
+    """b200gptq_pick_local on one rank: the framework's argmax over the valid columns (first maximum on ties, which
+    fp16 logits do produce), clamped, and the position advanced by one.  And the two-launch form for several ranks,
+    emulated on one GPU: each "rank" fills its slots of its own vector, their sum goes through b200gptq_pick_final."""
+    g = torch.Generator().manual_seed(rows + ld)
+    logits = (4 * torch.randn(rows, ld, generator=g)).half().to(DEV)
+    logits[0, valid // 2] = logits[0, : valid].max()          # a tie: the lower column wins
+    logits[:, valid:] = 1e4                                   # padding columns never win
+    tokens = torch.zeros(rows, dtype=torch.long, device=DEV)
+    pos = torch.tensor([41], dtype=torch.long, device=DEV)
+    ops.pick_local(logits, valid, 0, 1, 0, None, tokens, valid - 1, pos)
+    want = logits[:, :valid].float().argmax(dim=-1)
+    assert torch.equal(tokens, want) and int(pos) == 42
+    # four emulated ranks, each holding a quarter of the columns (the last one with padding)
+    world, per = 4, ld // 4 // 8 * 8
+    if per >= 8:
+        total = torch.zeros(rows, 4 * world, dtype=torch.float32, device=DEV)
+        for r in range(world):
+            part = logits[:, r * per:(r + 1) * per].contiguous()
+            v = max(1, min(per, valid - r * per))
+            slots = torch.full((rows, 4 * world), 7.0, dtype=torch.float16, device=DEV)
+            ops.pick_local(part, v, r * per, world, r, slots, None, valid - 1)
+            total += slots.float()
+        out = torch.zeros(rows, dtype=torch.long, device=DEV)
+        ops.pick_final(total.half(), world, out, valid - 1, pos)
+        cols = min(valid, world * per)
+        assert torch.equal(out, logits[:, :cols].float().argmax(dim=-1)) and int(pos) == 43
+
+
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("B,heads,pos", [(1, 8, 200), (2, 30, 200), (4, 30, 97), (8, 30, 255), (16, 24, 130), (3, 5, 0)])
 def test_single_query_attention_matches_fp32_softmax(hd, B, heads, pos):
