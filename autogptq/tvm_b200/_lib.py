@@ -32,6 +32,7 @@ _SIGNATURES = {
     "b200gptq_gemv_plan_run": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_gemv_plan_destroy": (None, [_c_void_p]),
     "b200gptq_gemv_path": (_c_int, [_c_int] * 6),
+    "b200gptq_gemm_split": (_c_int, [_c_int] * 4 + [_c_void_p] * 2),
     "b200gptq_gemm": (_c_int, [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p, _c_size_t, _c_void_p]),
     "b200gptq_sort_rows": (_c_int, [_c_void_p] * 3 + [_c_int] * 3 + [_c_void_p] * 3),
     "b200gptq_pack_fields": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]),

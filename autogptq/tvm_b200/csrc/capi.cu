@@ -39,6 +39,7 @@ int gemv_stream_dispatch(const __half*, const int32_t*, const int32_t*, const __
 int gemv_stream_dispatch_knobs(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*,
                                const __half*, __half*, int, int, int, int, int, void*, cudaStream_t, const int*);
 size_t gemm_workspace_bytes(int M, int K, int N, int bits);
+void gemm_split_query(int M, int K, int N, int* splits, int* ctas_per_sm);
 int gemm_dispatch(const __half*, const int32_t*, const int32_t*, const __half*, const int32_t*, const int32_t*,
                   const __half*, __half*, int, int, int, int, int, void*, size_t, cudaStream_t);
 
@@ -140,6 +141,16 @@ int b200gptq_gemv_path(int M, int K, int N, int bits, int group_size, int has_g_
     if (M < 1 || M > 8) return B200GPTQ_ERR_SHAPE;
     return (!has_g_idx && gemv_stream_supported(M, K, N, bits, group_size)) ? B200GPTQ_PATH_STREAM
                                                                            : B200GPTQ_PATH_GENERIC;
+}
+
+int b200gptq_gemm_split(int M, int K, int N, int bits, int* splits, int* ctas_per_sm) {
+    if (!splits || !ctas_per_sm) return B200GPTQ_ERR_NULL_POINTER;
+    int group_size = -1;
+    if (int st = check_layer(K, N, bits, &group_size)) return st;
+    if (bits != 3 && bits != 4) return B200GPTQ_ERR_BITS;
+    if (M < 1) return B200GPTQ_ERR_SHAPE;
+    gemm_split_query(M, K, N, splits, ctas_per_sm);
+    return B200GPTQ_OK;
 }
 
 int b200gptq_gemv(const void* x, const int32_t* qweight, const int32_t* qzeros, const void* scales,

@@ -676,6 +676,12 @@ size_t gemm_workspace_bytes(int M, int K, int N, int bits) {
     return kCounterBytes + (((size_t)M * K * sizeof(__half) + 255) & ~(size_t)255) + split_partial_bytes(M, N, K);
 }
 
+void gemm_split_query(int M, int K, int N, int* splits, int* ctas_per_sm) {
+    const GemmSplit g = pick_split(M, N, K);
+    *splits = g.splits;
+    *ctas_per_sm = g.per_sm;
+}
+
 int gemm_dispatch(const __half* x, const int32_t* qweight, const int32_t* qzeros, const __half* scales,
                   const int32_t* g_idx, const int32_t* x_perm, const __half* bias, __half* y, int M, int K, int N,
                   int bits, int group_size, void* workspace, size_t workspace_bytes, cudaStream_t stream) {

@@ -360,6 +360,15 @@ def attn_decode(q, k_cache, v_cache, pos, out, heads: int, hd: int):
     return out
 
 
+def gemm_split(M: int, K: int, N: int, bits: int):
+    """``b200gptq_gemm_split``: (thread blocks that share one tile's K, thread blocks per SM) of :func:`gemm` for this
+    problem on the current device.  Host-only."""
+    import ctypes
+    sp, per = ctypes.c_int(0), ctypes.c_int(0)
+    _lib.check(_lib.lib.b200gptq_gemm_split(M, K, N, bits, ctypes.byref(sp), ctypes.byref(per)), "b200gptq_gemm_split")
+    return sp.value, per.value
+
+
 def pick_local(logits, valid: int, base_index: int, world: int, rank: int, slots, tokens, max_token: int, pos_inc=None):
     """``b200gptq_pick_local``: greedy pick over this rank's fp16 ``logits[rows, ld]`` (columns ``[0, valid)``)."""
     _need_cuda("logits", logits, torch.float16)

@@ -208,6 +208,15 @@ B200GPTQ_API int b200gptq_gemm(const void* x, const int32_t* qweight, const int3
                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * How b200gptq_gemm divides this problem on the current device: *splits = thread blocks that share one tile's K
+ * (1 = none; their fp32 partial sums are added in a fixed order), *ctas_per_sm = 1 (three groups of weight warps per
+ * block) or 2 (one group, half of the shared and tensor memory).  Host-only; launches nothing.  The reference picks
+ * a tile per (bits, N, K, M bucket) from its tuned table (pycuda_warpper.py:77-127); this is the query for the
+ * corresponding decision here, so that a test can tell which form it exercised.
+ */
+B200GPTQ_API int b200gptq_gemm_split(int M, int K, int N, int bits, int* splits, int* ctas_per_sm);
+
+/*
  * Pack integer fields into GPTQ words: vals int32 [R, C] (R % 32 == 0, one field per element, packed
  * along R) -> out int32 [R/32*bits, C], bits in {2,3,4,8}.  This is the word-building half of
  * QuantLinear.pack of the reference (auto_gptq/nn_modules/qlinear.py:111-134 for qweight, called on

@@ -83,3 +83,20 @@ def test_registered_operator_has_a_shape_rule():
     with pytest.raises(Exception):
         op(torch.empty((5, K + 32), dtype=torch.float16, device="meta"), qweight, qzeros, scales, None, None, None,
            bits, 128, True)
+
+
+def test_gemm_work_split_rule():
+    """b200gptq_gemm_split is host-only (without a device it plans for 148 SMs): K is split only for up to 128 rows
+    and while every run keeps 16 k-tiles (40 above 64 rows); the second CTA per SM comes only for up to 64 rows and
+    only where it shortens waves x k-tiles."""
+    from autogptq.tvm_b200 import ops
+    assert ops.gemm_split(16, 4096, 4096, 4) == (4, 1)        # 32 column tiles on 148 SMs: four runs of 16 k-tiles
+    assert ops.gemm_split(128, 4096, 4096, 4) == (1, 1)       # 32 k-tiles per run would be too few above 64 rows
+    assert ops.gemm_split(128, 11008, 4096, 4) == (4, 1)      # 172 k-tiles: four runs of 43
+    assert ops.gemm_split(16, 4096, 12288, 4) == (3, 2)       # 96 tiles: three runs, two CTAs per SM
+    assert ops.gemm_split(64, 9216, 27648, 3) == (1, 2)       # 216 tiles: one wave of two per SM instead of two waves
+    assert ops.gemm_split(16, 9216, 9216, 3)[0] > 1
+    assert ops.gemm_split(256, 4096, 4096, 4) == (1, 1)       # more than one row tile: never split
+    assert ops.gemm_split(2048, 4096, 12288, 4) == (1, 1)
+    with pytest.raises(ValueError):
+        ops.gemm_split(16, 4095, 4096, 4)

@@ -49,6 +49,8 @@ GEMM_CASES = [
 
 @pytest.mark.parametrize("bits,K,N,gs,M,bias", GEMM_CASES)
 def test_gemm_vs_oracle(bits, K, N, gs, M, bias):
+    if N == 19200:
+        assert ops.gemm_split(M, K, N, bits)[1] == 2, "this case is meant to run two CTAs per SM"
     layer = synth.make_layer(bits, K, N, gs, False, bias=bias, seed=K + N + M)
     x = synth.make_x(M, K, seed=M)
     _, _, W = O.dequantize(*_layer_np(layer), bits)
@@ -75,6 +77,7 @@ def test_gemm_with_k_split_over_ctas_vs_oracle(bits, K, N, gs, M, bias):
     """Up to 128 rows and fewer column tiles than SMs: K is cut into runs, one CTA per run, and the last CTA of a
     tile to finish sums the fp32 partial sums in run order.  Same oracle and tolerance as the unsplit kernel; the
     result must not depend on which CTA arrives last, and the tile counters must be back at zero for the next call."""
+    assert ops.gemm_split(M, K, N, bits)[0] > 1, "this case is meant to run with K split over several CTAs"
     layer = synth.make_layer(bits, K, N, gs, False, bias=bias, seed=K + N + M)
     x = synth.make_x(M, K, seed=M)
     _, _, W = O.dequantize(*_layer_np(layer), bits)
@@ -103,7 +106,9 @@ def test_gemm_act_order_through_quantlinear(bits, K, N, gs, M):
 
 @pytest.mark.parametrize("M", [16, 128])
 def test_gemm_config2_vs_oracle(M):
-    """4-bit, K=4096, N=12288 (fused QKV), the prefill configuration, at the sizes the oracle finishes quickly."""
+    """4-bit, K=4096, N=12288 (fused QKV), the prefill configuration, at the sizes the oracle finishes quickly.
+    16 rows run as three runs of K on two CTAs per SM, 128 rows as one CTA per column tile."""
+    assert ops.gemm_split(M, 4096, 12288, 4) == ((3, 2) if M == 16 else (1, 1))
     layer = synth.make_layer(4, 4096, 12288, 128, False, seed=21)
     x = synth.make_x(M, 4096, seed=M)
     _, _, W = O.dequantize(*_layer_np(layer), 4)
